@@ -83,6 +83,14 @@ class CacheGroup:
     def window(self) -> Optional[int]:
         return self.spec.window
 
+    @property
+    def chunk(self) -> Optional[int]:
+        return getattr(self.spec, "chunk", None)
+
+    @property
+    def releases_pages(self) -> bool:
+        return self.window is not None or self.chunk is not None
+
 
 @dataclass
 class _Seq:
@@ -153,9 +161,12 @@ class CacheManager:
 
     def _first_needed_page(self, g: CacheGroup, next_pos: int) -> int:
         """Index of the first page that a token at position >= next_pos can still read."""
-        if g.window is None:
-            return 0
-        return max(0, next_pos - g.window + 1) // self.page_size
+        first = 0
+        if g.window is not None:
+            first = max(first, next_pos - g.window + 1)
+        if g.chunk:
+            first = max(first, next_pos // g.chunk * g.chunk)     # a token reads keys of its own chunk only
+        return first // self.page_size
 
     def pages_needed(self, rid, new_len: int) -> int:
         """Most pages any group has to add so that the request can hold `new_len` tokens."""
@@ -209,7 +220,7 @@ class CacheManager:
             raise CacheError(f"request {rid!r}: commit of {new_len} tokens outside what is reserved")
         s.length = new_len
         for gi, (g, t) in enumerate(zip(self.groups, s.tables)):
-            if g.window is None:
+            if not g.releases_pages:
                 continue
             first = min(self._first_needed_page(g, new_len), len(t))
             for i in range(first):

@@ -33,19 +33,29 @@ class CacheStorage:
         self.group_arrays: List[torch.Tensor] = []
         self.layer_kv: Dict[str, torch.Tensor] = {}
         for g in manager.groups:
-            arr = torch.zeros((len(g.layers), g.pool.total + 2, 2, g.spec.kv_heads, manager.page_size, g.spec.head_dim),
-                              dtype=dtype, device=self.device)
+            if g.spec.value_dim == g.spec.head_dim:
+                page_shape = (2, g.spec.kv_heads, manager.page_size, g.spec.head_dim)
+            else:                                   # keys [kv_heads, page, d], then values [kv_heads, page, dv]
+                page_shape = (g.spec.page_elems(manager.page_size),)
+            arr = torch.zeros((len(g.layers), g.pool.total + 2) + page_shape, dtype=dtype, device=self.device)
             for edge in (0, g.pool.total + 1):
                 arr[:, edge].view(torch.int16).fill_(GUARD_PATTERN)
             self.group_arrays.append(arr)
             for li, name in enumerate(g.layers):
                 self.layer_kv[name] = arr[li, 1:g.pool.total + 1]          # page -1 and page `total` are the guards
-        self.layer_state: Dict[str, torch.Tensor] = {}
-        for name, spec in manager.states.items():
+        # a layer's state: one tensor, or (for a mixer that keeps several) a dict of them, nested as its spec is
+        self.layer_state: Dict[str, object] = {}
+
+        def make(spec):
+            if isinstance(spec, dict):
+                return {k: make(v) for k, v in spec.items()}
             sdt = dtype if spec.dtype == "act" else getattr(torch, spec.dtype)
             # one row more than there are slots: the last row belongs to nobody (padding rows of a captured
             # decode step point at it, so that they disturb no request's state)
-            self.layer_state[name] = torch.zeros((manager.max_seqs + 1,) + tuple(spec.shape), dtype=sdt, device=self.device)
+            return torch.zeros((manager.max_seqs + 1,) + tuple(spec.shape), dtype=sdt, device=self.device)
+
+        for name, spec in manager.states.items():
+            self.layer_state[name] = make(spec)
         self.inert_slot = manager.max_seqs
         # the request slots' own rows (as many, plus nobody's): the token last drawn for the request, the sampler's
         # record (parameters, seed, count of draws: csrc/sampler.cu RbSampleParams) and its ring of recent tokens.
@@ -67,14 +77,28 @@ class CacheStorage:
 
     def zero_slot(self, slot: int) -> None:
         """A fixed-size state starts at zero when its request is admitted."""
-        for t in self.layer_state.values():
+        for t in self.state_tensors():
             t[slot].zero_()
+
+    def state_tensors(self) -> List[torch.Tensor]:
+        out: List[torch.Tensor] = []
+
+        def walk(x):
+            if isinstance(x, dict):
+                for v in x.values():
+                    walk(v)
+            else:
+                out.append(x)
+
+        for s in self.layer_state.values():
+            walk(s)
+        return out
 
     def bytes(self) -> int:
         return sum(a.numel() * a.element_size() for a in self.group_arrays) + \
-            sum(a.numel() * a.element_size() for a in self.layer_state.values())
+            sum(a.numel() * a.element_size() for a in self.state_tensors())
 
     @staticmethod
     def bytes_per_page(manager_groups, page_size: int, dtype: torch.dtype) -> int:
         isz = torch.empty((), dtype=dtype).element_size()
-        return sum(len(g.layers) * 2 * g.spec.kv_heads * page_size * g.spec.head_dim * isz for g in manager_groups)
+        return sum(len(g.layers) * g.spec.page_elems(page_size) * isz for g in manager_groups)

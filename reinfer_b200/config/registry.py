@@ -55,9 +55,10 @@ def architecture_name(config: Mapping[str, Any]) -> str:
     archs = config.get("architectures")
     if isinstance(archs, list) and archs and isinstance(archs[0], str):
         return archs[0]
-    mt = config.get("model_type")
-    if isinstance(mt, str):
-        return mt
+    for key in ("architecture", "model_type"):         # a single name in place of the list
+        mt = config.get(key)
+        if isinstance(mt, str):
+            return mt
     raise MissingKey("architectures")
 
 
@@ -76,6 +77,11 @@ def load_config(model_dir: str):
     with open(path, "r", encoding="utf-8") as f:
         raw = json.load(f)
     arch = resolve_architecture(raw)
+    if getattr(arch.config_cls, "reads_tensor_shapes", False):
+        # a configuration that leaves some sizes to the checkpoint gets the tensors' shapes (headers only)
+        from ..weights.safetensors_io import open_model_tensors
+        found = open_model_tensors(model_dir)
+        return arch, arch.config_cls.from_dict(raw, {n: tuple(f.shape(k)) for n, (f, k) in found.items()})
     return arch, arch.config_cls.from_dict(raw)
 
 
@@ -111,3 +117,5 @@ def _ensure_builtin() -> None:
     _builtin_done = True
     from ..models import qwen3 as _q  # registers itself on import
     _q.register()
+    from ..models import silutar as _s
+    _s.register()

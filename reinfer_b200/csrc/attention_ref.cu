@@ -6,6 +6,9 @@
 // cut into steps, on the batch, or on the page size - so this kernel gives the same
 // bits under every cut.  It is the attention of the 32-bit path and the yardstick of
 // the faster bfloat16 kernels.
+// Beyond the plain form it takes: a value head size of its own (dv != d), a chunk mask (a token sees the
+// keys of its own chunk of `chunk` positions, counted from position 0), a logarithmic distance penalty per
+// query head (score -= r1[h] * ln(1 + r2[h] * (i - j))), and a factor on the output.
 // (reference semantics: crates/cuda/kernels/decode_gqa_kernels.cu:99-136 page lookup
 //  page[t/block_len]; decode_flash_kernels.cu:212-349 max/exp/sum/PV in f32.)
 #include "common.cuh"
@@ -13,17 +16,20 @@
 #define RA_WARPS 4
 #define RA_MAX_D 512
 
-// q        [T, QH, d]
-// cache    one layer: [page][2][KH][page_size][d]
+// q        [T, QH, d];  out [T, QH, dv]
+// cache    one layer: [page][ K: [KH][page_size][d] | V: [KH][page_size][dv] ]   (dv == d: [page][2][KH][page_size][d])
 // block_table [rows, max_pages] (page id of the i-th page of a request's row)
 // tok_row  [T] row of block_table for token t;  positions [T] absolute position of token t
-// A token at position p attends keys max(0, p-window+1) .. p  (window <= 0: all of them).
+// A token at position p attends keys max(0, p-window+1) .. p  (window <= 0: all of them); with chunk > 0 also
+// only keys from floor(p / chunk) * chunk on.
 template <typename TA, typename TC>
 __global__ void __launch_bounds__(RA_WARPS * 32)
 paged_attention_ref_kernel(const TA* __restrict__ q, const TC* __restrict__ cache,
                            const int* __restrict__ block_table, const int* __restrict__ tok_row,
                            const int* __restrict__ positions, TA* __restrict__ out,
-                           int QH, int KH, int d, int page_size, int max_pages, int window, float scale) {
+                           int QH, int KH, int d, int dv, int page_size, int max_pages, int window, float scale,
+                           int chunk, const float* __restrict__ r1, const float* __restrict__ r2, float out_scale) {
+    pdl_trigger(); pdl_wait();
     extern __shared__ float qs_all[];                         // RA_WARPS * d floats
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
@@ -35,10 +41,13 @@ paged_attention_ref_kernel(const TA* __restrict__ q, const TC* __restrict__ cach
     __syncwarp();
     const int kh = hq / (QH / KH);
     const int pos = positions[t];
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    if (chunk > 0) lo = max(lo, pos / chunk * chunk);
+    const float pen1 = r1 ? r1[hq] : 0.0f, pen2 = r1 ? r2[hq] : 0.0f;
     const int* bt = block_table + (size_t)tok_row[t] * max_pages;
-    const size_t head_stride = (size_t)page_size * d;         // one (page, k|v, head) tile
-    const size_t page_stride = 2 * (size_t)KH * head_stride;
+    const size_t head_stride = (size_t)page_size * d;         // one (page, k, head) tile
+    const size_t vhead_stride = (size_t)page_size * dv;       // one (page, v, head) tile
+    const size_t page_stride = (size_t)KH * (head_stride + vhead_stride);
 
     constexpr int NACC = RA_MAX_D / 32;
     float acc[NACC];
@@ -56,10 +65,11 @@ paged_attention_ref_kernel(const TA* __restrict__ q, const TC* __restrict__ cach
         if (valid) {
             const int off = key % page_size;
             const TC* krow = cache + (size_t)page * page_stride + (size_t)kh * head_stride + (size_t)off * d;
-            vrow = krow + (size_t)KH * head_stride;
+            vrow = cache + (size_t)page * page_stride + (size_t)KH * head_stride + (size_t)kh * vhead_stride + (size_t)off * dv;
             float dot = 0.0f;
             for (int i = 0; i < d; ++i) dot = fmaf(qs[i], to_f32(krow[i]), dot);
             s = dot * scale;
+            if (r1) s -= pen1 * log1pf(pen2 * (float)(pos - key));
         }
         const float bm = warp_max(s);
         if (bm == -INFINITY) continue;                         // no key in this block (warp-uniform)
@@ -77,39 +87,42 @@ paged_attention_ref_kernel(const TA* __restrict__ q, const TC* __restrict__ cach
 #pragma unroll
             for (int i = 0; i < NACC; ++i) {
                 const int dim = lane + 32 * i;
-                if (dim < d) acc[i] = fmaf(pj, to_f32(vr[dim]), acc[i]);
+                if (dim < dv) acc[i] = fmaf(pj, to_f32(vr[dim]), acc[i]);
             }
         }
         m = m_new;
     }
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-    TA* op = out + ((size_t)t * QH + hq) * d;
+    TA* op = out + ((size_t)t * QH + hq) * dv;
 #pragma unroll
     for (int i = 0; i < NACC; ++i) {
         const int dim = lane + 32 * i;
-        if (dim < d) op[dim] = from_f32<TA>(acc[i] * inv);
+        if (dim < dv) op[dim] = from_f32<TA>(out_scale == 1.0f ? acc[i] * inv : acc[i] * inv * out_scale);
     }
 }
 
+// dv: the value heads' size (0: as d).  chunk 0: no chunk mask.  r1, r2 [QH] float: the distance penalty (null: none).
 extern "C" int rb_paged_attention_ref(const void* q, const void* cache, int dtype,
                                       const int* block_table, const int* tok_row, const int* positions,
                                       void* out, int n_tokens, int QH, int KH, int d, int page_size,
-                                      int max_pages, int window, float scale, void* stream) {
+                                      int max_pages, int window, float scale, int dv, int chunk, const float* r1,
+                                      const float* r2, float out_scale, void* stream) {
     if (n_tokens <= 0) return 0;
+    if (dv <= 0) dv = d;
     if (QH <= 0 || KH <= 0 || QH % KH != 0) RB_REFUSE("attention: %d query heads over %d kv heads", QH, KH);
-    if (d <= 0 || d > RA_MAX_D) RB_REFUSE("attention: head_dim %d (supported: 1..%d)", d, RA_MAX_D);
+    if (d <= 0 || d > RA_MAX_D || dv > RA_MAX_D) RB_REFUSE("attention: head sizes %d, %d (supported: 1..%d)", d, dv, RA_MAX_D);
     if (page_size <= 0 || max_pages <= 0) RB_REFUSE("attention: page_size %d max_pages %d", page_size, max_pages);
+    if (chunk < 0 || (r1 == nullptr) != (r2 == nullptr)) RB_REFUSE("attention: chunk %d, or half a distance penalty", chunk);
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_tokens, rb_ceil_div(QH, RA_WARPS));
     const size_t smem = (size_t)RA_WARPS * d * sizeof(float);
     if (dtype == RB_F32)
-        paged_attention_ref_kernel<float, float><<<grid, RA_WARPS * 32, smem, s>>>(
+        return rb_launch(paged_attention_ref_kernel<float, float>, grid, dim3(RA_WARPS * 32), smem, s,
             (const float*)q, (const float*)cache, block_table, tok_row, positions, (float*)out,
-            QH, KH, d, page_size, max_pages, window, scale);
-    else if (dtype == RB_BF16)
-        paged_attention_ref_kernel<bf16, bf16><<<grid, RA_WARPS * 32, smem, s>>>(
+            QH, KH, d, dv, page_size, max_pages, window, scale, chunk, r1, r2, out_scale);
+    if (dtype == RB_BF16)
+        return rb_launch(paged_attention_ref_kernel<bf16, bf16>, grid, dim3(RA_WARPS * 32), smem, s,
             (const bf16*)q, (const bf16*)cache, block_table, tok_row, positions, (bf16*)out,
-            QH, KH, d, page_size, max_pages, window, scale);
-    else RB_REFUSE("attention: dtype %d", dtype);
-    return RB_LAUNCH_RESULT();
+            QH, KH, d, dv, page_size, max_pages, window, scale, chunk, r1, r2, out_scale);
+    RB_REFUSE("attention: dtype %d", dtype);
 }

@@ -157,7 +157,7 @@ class Engine:
         (crates/memory/src/budget.rs:99-155)."""
         from ..cache.manager import group_layers
         isz = 4 if self.dtype == torch.float32 else 2
-        per_page = sum(len(n) * 2 * s.kv_heads * self.page_size * s.head_dim * isz for s, n in group_layers(paged))
+        per_page = sum(len(n) * s.page_elems(self.page_size) * isz for s, n in group_layers(paged))
         if per_page == 0:
             return 1
         free, total = torch.cuda.mem_get_info(self.device)
@@ -340,6 +340,12 @@ class Engine:
                 if not 0 <= int(w) < len(e.tokens):
                     raise EngineError(f"request {e.request_id!r}: wanted place {w} outside its {len(e.tokens)} tokens")
         cm = self.cache
+        limit = getattr(self.model.embedding, "max_positions", None)
+        if limit:
+            for e in entries:
+                cur = cm.length(e.request_id) if e.request_id in cm else 0
+                if cur + len(e.tokens) > limit:
+                    raise EngineError(f"request {e.request_id!r}: {cur + len(e.tokens)} tokens, the model has {limit} positions")
         # enough slots and pages for the whole batch, before anything is changed
         new = [e for e in entries if e.request_id not in cm]
         if len(new) > cm.free_slots():

@@ -170,13 +170,20 @@ def _need(cond: bool, msg: str) -> None:
 
 # ------------------------------------------------------------------ wrappers
 def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, slot_token: Optional[torch.Tensor] = None,
-                 entry_slot: Optional[torch.Tensor] = None, tok_entry: Optional[torch.Tensor] = None) -> None:
+                 entry_slot: Optional[torch.Tensor] = None, tok_entry: Optional[torch.Tensor] = None,
+                 pos_table: Optional[torch.Tensor] = None, positions: Optional[torch.Tensor] = None) -> None:
     """out[t,:] (float32) = table[ids[t],:]; where ids[t] < 0 and the slot tables are given, the id is
-    slot_token[entry_slot[tok_entry[t]]]: the token that the sampler left in the request's slot."""
+    slot_token[entry_slot[tok_entry[t]]]: the token that the sampler left in the request's slot.  With a table of
+    learned position vectors (the embedding table's dtype) the row pos_table[positions[t]] is added."""
     _need(out.dtype == torch.float32 and ids.dtype == torch.int32, "embed_gather: out float32, ids int32")
     _need(table.is_contiguous() and out.is_contiguous(), "embed_gather: contiguous tensors")
+    if pos_table is not None:
+        _need(pos_table.dtype == table.dtype and pos_table.is_contiguous() and pos_table.shape[1] == table.shape[1] and
+              positions is not None, "embed_gather: a position table of the embedding's dtype and width, with positions")
     _check(lib().rb_embed_gather(_p(table), dt(table), _p(ids), _p(slot_token), _p(entry_slot), _p(tok_entry), _p(out),
-                                 c_int(ids.numel()), c_int(table.shape[1]), c_int(table.shape[0]), _stream()), "embed_gather")
+                                 c_int(ids.numel()), c_int(table.shape[1]), c_int(table.shape[0]),
+                                 _p(pos_table), _p(positions if pos_table is not None else None),
+                                 c_int(pos_table.shape[0] if pos_table is not None else 0), _stream()), "embed_gather")
 
 
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor, out: torch.Tensor,
@@ -283,13 +290,24 @@ def gemm_ref(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: bool
 
 def paged_attention_ref(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, tok_row: torch.Tensor,
                         positions: torch.Tensor, out: torch.Tensor, QH: int, KH: int, d: int, page_size: int,
-                        window: int, scale: float, work=(0.0, 0.0)) -> None:
+                        window: int, scale: float, work=(0.0, 0.0), dv: int = 0, chunk: int = 0,
+                        penalty=None, out_scale: float = 1.0) -> None:
+    """The plain attention over the paged cache.  dv: the value heads' size where it differs from d (the cache of a
+    layer is then [page][K: KH x page x d | V: KH x page x dv]); chunk: a token sees only the keys of its own chunk
+    of that many positions; penalty = (r1, r2), float32 [QH] each: score -= r1 ln(1 + r2 (i - j)); out_scale
+    multiplies the output before it is rounded."""
     _need(q.is_contiguous() and out.is_contiguous() and cache.is_contiguous() and block_table.is_contiguous(),
           "attention: contiguous")
     _need(q.dtype == cache.dtype == out.dtype, "attention: one dtype for q, cache and out")
+    r1 = r2 = None
+    if penalty is not None:
+        r1, r2 = penalty
+        _need(r1.dtype == torch.float32 and r2.dtype == torch.float32 and r1.numel() == QH and r2.numel() == QH,
+              "attention: the distance penalty is two float32 vectors, one number per query head each")
     _check(lib().rb_paged_attention_ref(_p(q), _p(cache), c_int(dt(q)), _p(block_table), _p(tok_row), _p(positions),
                                         _p(out), c_int(q.shape[0]), c_int(QH), c_int(KH), c_int(d), c_int(page_size),
-                                        c_int(block_table.shape[1]), c_int(window), c_float(scale), _stream()),
+                                        c_int(block_table.shape[1]), c_int(window), c_float(scale), c_int(dv), c_int(chunk),
+                                        _p(r1), _p(r2), c_float(out_scale), _stream()),
            "paged_attention_ref", *work)
 
 
@@ -826,6 +844,118 @@ def gemm_bf16_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor
                                      c_int(splits), nw, nb, *_row_scale_args(row_scale, T), _stream()),
            f"gemm+swiglu {2 * F_}x{K}", 4.0 * T * F_ * K, 2.0 * (T * K + 2 * F_ * K + T * F_))
     return True
+
+
+# ------------------------------------------------------------------ statistics-free norm, soft cap, short convolution, recurrences
+def dyt(x: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor, b: torch.Tensor, alpha: torch.Tensor,
+        out: torch.Tensor, row_idx: Optional[torch.Tensor] = None) -> None:
+    """x (float32 [rows, h]) += delta (x's shape or a stack of partial sums, float32, added in ascending order);
+    out[r] = tanh(alpha x[row_idx[r] or r]) w + b.  With row_idx x itself stays as it is."""
+    _need(x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous(), "dyt: x float32 contiguous")
+    _need(w.dtype == b.dtype == alpha.dtype and alpha.numel() == 1, "dyt: weight, bias and alpha of one dtype")
+    h = x.shape[-1]
+    rows = out.numel() // h
+    n_delta = 0
+    if delta is not None:
+        _need(delta.dtype == torch.float32 and delta.is_contiguous() and delta.numel() % x.numel() == 0 and delta.shape[-1] == h,
+              "dyt: delta float32 with x's shape (or a stack of it)")
+        n_delta = delta.numel() // x.numel()
+    _check(lib().rb_dyt(_p(x), _p(delta), c_int(n_delta), c_longlong(x.numel()), _p(w), _p(b), _p(alpha), c_int(dt(w)),
+                        _p(out), c_int(dt(out)), _p(row_idx), c_int(rows), c_int(h), _stream()), "dyt",
+           0.0, float(rows * h * (4 + out.element_size())))
+
+
+def softcap(x: torch.Tensor, cap: float) -> None:
+    """x <- cap tanh(x / cap) in place (float32)."""
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "softcap: float32 contiguous")
+    _check(lib().rb_softcap(_p(x), c_longlong(x.numel()), c_float(cap), _stream()), "softcap")
+
+
+def tanh_(x: torch.Tensor) -> None:
+    """tanh in place on a block [rows, cols] whose rows may be strided."""
+    _need(x.dim() == 2 and x.stride(1) == 1, "tanh_: rows contiguous")
+    _check(lib().rb_unary(_p(x), c_int(dt(x)), c_longlong(x.stride(0)), c_int(x.shape[0]), c_int(x.shape[1]), c_int(0),
+                          _stream()), "tanh")
+
+
+def head_norm_gate(o: torch.Tensor, w: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, H: int, dv: int, eps: float,
+                   gate_fn: str, out_scale: float = 1.0) -> None:
+    """o [T, H, dv] float32 -> out [T, H*dv] (rows may be strided): o over its root mean square per head, times w
+    ([dv]: one weight for all heads; [H*dv]: one per head), times sigmoid or silu of gate [T, H*dv], times out_scale."""
+    T = o.shape[0]
+    _need(o.dtype == torch.float32 and o.is_contiguous() and w.dtype == torch.float32 and w.numel() in (dv, H * dv),
+          "head_norm_gate: o and w float32, w one row or one per head")
+    _need(gate.dtype == out.dtype and gate.stride(1) == 1 and out.stride(1) == 1, "head_norm_gate: gate and out of one dtype")
+    _check(lib().rb_head_norm_gate(_p(o), _p(w), c_int(int(w.numel() == H * dv and H > 1)), _p(gate), c_longlong(gate.stride(0)),
+                                   c_int({"sigmoid": 0, "silu": 1}[gate_fn]), _p(out), c_longlong(out.stride(0)),
+                                   c_int(dt(out)), c_int(T), c_int(H), c_int(dv), c_float(eps), c_float(out_scale),
+                                   _stream()), "head_norm_gate", 0.0, float(T * H * dv * (4 + 2 * out.element_size())))
+
+
+def shortconv(u: torch.Tensor, w: torch.Tensor, state: torch.Tensor, y: torch.Tensor, cu_q: torch.Tensor,
+              entry_slot: torch.Tensor, n_entries: int, max_q_len: int, silu: bool) -> None:
+    """y[t, c] = act(sum_j w[c, j] u[t - taps + 1 + j, c]) per request; inputs before the step come from the request's
+    slot in state [slots, taps-1, C] float32 (zeros for a new request), which is left holding the last taps-1 inputs."""
+    C, taps = w.shape
+    _need(w.dtype == torch.float32 and w.is_contiguous() and state.dtype == torch.float32 and state.is_contiguous(),
+          "shortconv: float32 taps and state")
+    _need(u.shape[1] == C and y.shape[1] == C and u.stride(1) == 1 and y.stride(1) == 1 and u.dtype == y.dtype,
+          "shortconv: u and y [T, C] of one dtype")
+    _need(tuple(state.shape[1:]) == (taps - 1, C), "shortconv: state [slots, taps-1, C]")
+    _check(lib().rb_shortconv(_p(u), c_longlong(u.stride(0)), _p(w), _p(state), _p(y), c_longlong(y.stride(0)), c_int(dt(u)),
+                              _p(cu_q), _p(entry_slot), c_int(n_entries), c_int(max_q_len), c_int(C), c_int(taps),
+                              c_int(int(silu)), _stream()), "shortconv", 0.0, float(2 * u.shape[0] * C * u.element_size()))
+
+
+def unit_heads_append(x: torch.Tensor, kv_slot: Optional[torch.Tensor], q_out: torch.Tensor, cache: torch.Tensor,
+                      QH: int, KH: int, dk: int, dv: int, page_size: int, eps: float) -> None:
+    """x [T, (QH+KH) dk + KH dv]: q and k heads over their root mean square (no weight), q -> q_out [T, QH, dk],
+    k and v into the token's cache slot (layout of paged_attention_ref with dv)."""
+    _need(x.stride(1) == 1 and x.shape[1] == (QH + KH) * dk + KH * dv and q_out.is_contiguous() and x.dtype == q_out.dtype == cache.dtype,
+          "unit_heads_append: x [T, q|k|v], one dtype")
+    _check(lib().rb_unit_heads_append(_p(x), c_longlong(x.stride(0)), _p(kv_slot), _p(q_out), _p(cache), c_int(dt(x)),
+                                      c_int(x.shape[0]), c_int(QH), c_int(KH), c_int(dk), c_int(dv), c_int(page_size),
+                                      c_float(eps), _stream()), "unit_heads_append")
+
+
+def chunk_attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch.Tensor, QH: int, KH: int, dk: int, dv: int,
+                    chunk: int, scale: float, penalty, out_scale: float = 1.0) -> None:
+    """Attention of a step's tokens over the keys of their own chunk, with the logarithmic distance penalty
+    (parts/chunk_attention.py).  q [T, QH, dk], out [T, QH, dv]."""
+    paged_attention_ref(q, cache, group.block_table, ctx.tok_entry, ctx.positions, out, QH, KH, dk, group.page_size, 0, scale,
+                        dv=dv, chunk=chunk, penalty=penalty, out_scale=out_scale)
+
+
+RECURRENCE_FORMS = {"diagonal": 0, "delta_old_state": 1, "delta_gated_state": 2}
+RECURRENCE_GATES = {"sigmoid_root": 0, "exp_sigmoid": 1, "exp_softplus": 2}
+
+
+def recurrence(form: str, gate: str, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
+               z_bias: Optional[torch.Tensor], state: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor,
+               entry_slot: torch.Tensor, n_entries: int, H: int, Hk: int, dk: int, dv: int, *, gate_param: float = 0.0,
+               q_scale: float = 1.0, unit_qk: bool = False, a_pre: Optional[torch.Tensor] = None,
+               a_bias: Optional[torch.Tensor] = None, b_pre: Optional[torch.Tensor] = None,
+               rate: Optional[torch.Tensor] = None) -> None:
+    """The token-by-token recurrence over state [slots, H, dk, dv] (float32) of csrc/recurrence.cu.  q, k [T, Hk*dk],
+    v [T, H*dv], a_pre [T, H*dk], b_pre [T, H] in the activation dtype (rows may be strided); z [T, H*dk] float32;
+    z_bias, a_bias [H*dk] and rate [H] float32; out [T, H, dv] float32."""
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, dk, dv),
+          "recurrence: state float32 [slots, H, dk, dv]")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and z.dtype == torch.float32, "recurrence: out and z float32")
+    for t in (q, k, v, z, a_pre, b_pre):
+        _need(t is None or t.stride(-1) == 1, "recurrence: rows contiguous")
+    _need(q.dtype == k.dtype == v.dtype, "recurrence: q, k, v of one dtype")
+    for t in (z_bias, a_bias, rate):
+        _need(t is None or (t.dtype == torch.float32 and t.is_contiguous()), "recurrence: small vectors float32")
+    ld = lambda t: c_longlong(t.stride(0) if t is not None else 0)
+    T = q.shape[0]
+    _check(lib().rb_recurrence(c_int(RECURRENCE_FORMS[form]), c_int(RECURRENCE_GATES[gate]), c_int(dt(q)),
+                               _p(q), ld(q), _p(k), ld(k), _p(v), ld(v), _p(z), ld(z), _p(z_bias),
+                               _p(a_pre), ld(a_pre), _p(a_bias), _p(b_pre), ld(b_pre), _p(rate),
+                               c_float(gate_param), c_float(q_scale), c_int(int(unit_qk)),
+                               _p(state), _p(out), _p(cu_q), _p(entry_slot), c_int(n_entries), c_int(H), c_int(Hk),
+                               c_int(dk), c_int(dv), _stream()), f"recurrence {form}",
+           6.0 * T * H * dk * dv, float(T * H * (2 * dk + 2 * dv) * 4 + 2 * n_entries * H * dk * dv * 4))
 
 
 def random_normal(out: torch.Tensor, base: int, mean: float, std: float) -> None:

@@ -39,10 +39,22 @@ from .spec import PartSpec
 
 @dataclass(frozen=True)
 class PagedKVSpec:
-    """Keys and values of every token (or of the last `window` tokens) in pages."""
+    """Keys and values of every token in pages - or only of the last `window` tokens, or only of the tokens in the
+    present chunk of `chunk` positions (chunks counted from position 0): pages that no later token can read go back
+    to the pool.  `v_head_dim`: the value heads' size where it differs from the keys' (None: the same)."""
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
+    chunk: Optional[int] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
+
+    def page_elems(self, page_size: int) -> int:
+        """Elements of one page of one layer: the keys [kv_heads, page, head_dim], then the values."""
+        return self.kv_heads * page_size * (self.head_dim + self.value_dim)
 
 
 @dataclass(frozen=True)
@@ -133,7 +145,9 @@ class Mixer(Part):
     def cache_spec(self) -> Optional[PagedKVSpec]:
         return None
 
-    def state_spec(self) -> Optional[SlotStateSpec]:
+    def state_spec(self):
+        """None, one SlotStateSpec (the layer's `cache.state` is then a tensor [slots, *shape]), or a dict
+        name -> SlotStateSpec | dict (then `cache.state` is a dict of the same shape holding tensors)."""
         return None
 
     def prepare(self, device, dtype) -> None:
@@ -179,3 +193,4 @@ def _ensure_builtin() -> None:
         return
     _done = True
     from . import norm, rope, attention, ffn, embedding, block  # noqa: F401  (each registers itself)
+    from . import dyt, chunk_attention, linear_recurrence, parallel  # noqa: F401

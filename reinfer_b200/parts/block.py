@@ -60,4 +60,26 @@ def _norm(norm, reader, ctx, x, delta):
     return norm.forward(ctx, x, delta=delta)
 
 
+class PreNormMixerBlock:
+    """x += mixer(mixer_norm(x)) and nothing else: a layer without a feed-forward."""
+    roles = ("mixer_norm", "mixer")
+    hands_on_sums = True
+
+    def __init__(self, parts):
+        need_roles("prenorm_mixer", parts, self.roles)
+        self.mixer_norm, self.mixer = (parts[r] for r in self.roles)
+
+    def forward(self, ctx, x, cache, delta=None):
+        xn = _norm(self.mixer_norm, self.mixer, ctx, x, delta)
+        ctx.norm_ahead = getattr(ctx, "norm_after_block", None)
+        try:
+            return self.mixer.forward(ctx, xn, x, cache)
+        finally:
+            ctx.norm_ahead = None
+
+    def entry_norm(self):
+        return self.mixer_norm if _prepares(self.mixer_norm, self.mixer) else None
+
+
 register_part("block", "prenorm", PreNormBlock)
+register_part("block", "prenorm_mixer", PreNormMixerBlock)

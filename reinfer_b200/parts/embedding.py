@@ -14,19 +14,39 @@ from .linear import matmul
 
 
 class Embedding(Part):
-    def __init__(self, vocab: int, hidden: int):
-        self.vocab, self.hidden = int(vocab), int(hidden)
+    """`positions` > 0: a table of that many learned position vectors (tensor `positions_name`) whose row for the
+    token's position is added to the token's row, unscaled, in the same kernel.  `table_name`: the local name of
+    the token table (a tied output head takes the table under this name)."""
+
+    def __init__(self, vocab: int, hidden: int, positions: int = 0, table_name: str = "weight",
+                 positions_name: str = "positions.weight"):
+        self.vocab, self.hidden, self.positions = int(vocab), int(hidden), int(positions)
+        self.table_name, self.positions_name = str(table_name), str(positions_name)
         self.weight = None
+        self.pos_weight = None
 
     def param_specs(self):
-        return {"weight": ParamSpec((self.vocab, self.hidden), init="table")}
+        out = {self.table_name: ParamSpec((self.vocab, self.hidden), init="table")}
+        if self.positions:
+            out[self.positions_name] = ParamSpec((self.positions, self.hidden), init="table")
+        return out
 
     def bind(self, tensors):
-        self.weight = tensors["weight"]
+        self.weight = tensors[self.table_name]
+        if self.positions:
+            self.pos_weight = tensors[self.positions_name]
+            if self.pos_weight.dtype != self.weight.dtype:
+                self.pos_weight = self.pos_weight.to(self.weight.dtype)
+
+    @property
+    def max_positions(self):
+        """The longest request the embedding can place (None: no limit of its own)."""
+        return self.positions or None
 
     def forward(self, ctx) -> torch.Tensor:
         x = torch.empty((ctx.n_tokens, self.hidden), dtype=torch.float32, device=ctx.device)
-        ops.embed_gather(self.weight, ctx.token_ids, x, ctx.slot_token, ctx.entry_slot, ctx.tok_entry)
+        ops.embed_gather(self.weight, ctx.token_ids, x, ctx.slot_token, ctx.entry_slot, ctx.tok_entry,
+                         pos_table=self.pos_weight, positions=ctx.positions)
         return x
 
 
@@ -34,8 +54,9 @@ class LMHead(Part):
     """`tied`: the embedding table is the output matrix; the model hands it over in bind()
     under the local name 'weight' either way."""
 
-    def __init__(self, vocab: int, hidden: int, tied: bool = False, fallback: str = ""):
+    def __init__(self, vocab: int, hidden: int, tied: bool = False, fallback: str = "", softcap: float = 0.0):
         self.vocab, self.hidden, self.tied, self.fallback = int(vocab), int(hidden), bool(tied), fallback
+        self.softcap = float(softcap or 0.0)        # > 0: logits <- cap * tanh(logits / cap)
         self.weight = None
 
     def param_specs(self):
@@ -47,7 +68,10 @@ class LMHead(Part):
         self.weight = tensors["weight"]
 
     def forward(self, ctx, xn_rows: torch.Tensor) -> torch.Tensor:
-        return matmul(ctx, xn_rows, self.weight, out_dtype=torch.float32)
+        logits = matmul(ctx, xn_rows, self.weight, out_dtype=torch.float32)
+        if self.softcap > 0.0:
+            ops.softcap(logits, self.softcap)
+        return logits
 
 
 register_part("embedding", "embedding", Embedding)

@@ -14,22 +14,25 @@ from .linear import matmul, matmul_into_residual, takes_row_scaled
 
 
 class SwiGLU(FeedForward):
-    def __init__(self, hidden: int, intermediate: int):
+    def __init__(self, hidden: int, intermediate: int, names=("gate_proj.weight", "up_proj.weight", "down_proj.weight")):
+        """names: the local tensor names of the gate, up and down matrices."""
         self.hidden, self.inter = int(hidden), int(intermediate)
+        self.names = tuple(names)
         self.w_gate_up = None
         self.w_down = None
 
     def param_specs(self):
-        return {"gate_proj.weight": ParamSpec((self.inter, self.hidden)),
-                "up_proj.weight": ParamSpec((self.inter, self.hidden)),
-                "down_proj.weight": ParamSpec((self.hidden, self.inter))}
+        g, u, d = self.names
+        return {g: ParamSpec((self.inter, self.hidden)),
+                u: ParamSpec((self.inter, self.hidden)),
+                d: ParamSpec((self.hidden, self.inter))}
 
     def bind(self, tensors):
-        g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        g, u = tensors[self.names[0]], tensors[self.names[1]]
         if g.dtype != u.dtype:
             g, u = g.float(), u.float()
         self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
-        self.w_down = tensors["down_proj.weight"]
+        self.w_down = tensors[self.names[2]]
 
     @property
     def takes_row_scaled(self) -> bool:

@@ -119,7 +119,7 @@ class Model:
                 elif not ps.optional:
                     raise KeyError(f"tensor {g} was not loaded")
             if part is self.lm_head and getattr(part, "tied", False):
-                local["weight"] = state[self.spec.embedding.prefix + "weight"]
+                local["weight"] = state[self.spec.embedding.prefix + getattr(self.embedding, "table_name", "weight")]
             part.bind(local)
 
     def prepare(self, device, dtype) -> None:

@@ -28,7 +28,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens that live requests hold at any time (each rounded up to 64)")
     ap.add_argument("--page-size", type=int, default=64)
-    ap.add_argument("--max-num-seqs", type=int, default=8)
+    ap.add_argument("--max-num-seqs", type=int, default=4, help="request slots (rows of per-request state)")
     args = ap.parse_args(argv)
 
     print("trace_run: loading torch and the kernel library ...", file=sys.stderr, flush=True)
