@@ -10,6 +10,7 @@
 // each in registers, and the two dot products per token are completed by two shuffles in a fixed order.
 // The CTA walks its request's tokens of this step in order; per tile of tokens all threads first prepare
 // the token vectors in shared memory - the gate from its pre-activation, unit vectors, scales - in float:
+// (a gate is held as g - 1 = expm1(ln g) and applied as S + (g - 1) S, so that a gate near 1 keeps its digits)
 //   gate 0:  g = sigmoid(z)^(1/tau)                 = exp(-softplus(-z) / tau)
 //   gate 1:  g = exp(-c * sigmoid(z))
 //   gate 2:  g = exp(-exp(rate[h]) * softplus(z))
@@ -99,16 +100,20 @@ recurrence_kernel(const RecurArgs A) {
             }
             for (int i = lane; i < RR_SPLIT * RP; i += 32) {
                 const int at = tt * VEC + (i / RP) * RPP + (i % RP);
-                float qv = 0.0f, kv = 0.0f, g = 0.0f, uv = 0.0f, av = 0.0f;
+                float qv = 0.0f, kv = 0.0f, g = -1.0f, uv = 0.0f, av = 0.0f;
                 if (i < dk) {
                     qv = to_f32(qr[i]) * qn;
                     const float kraw = to_f32(kr[i]);
                     kv = kraw * kn;
                     float z = A.z[t * A.ldz + (size_t)h * dk + i];
                     if (A.z_bias) z += A.z_bias[(size_t)h * dk + i];
-                    if (A.gate == 0) g = expf(-softplus_f(-z) * A.gate_param);
-                    else if (A.gate == 1) g = expf(-A.gate_param * sigmoid_f(z));
-                    else g = expf(-rate * softplus_f(z));
+                    // the gate is kept as g - 1 = expm1(ln g): a gate close to 1 (a memory that lasts thousands of
+                    // tokens) then keeps the digits of 1 - g that rounding g itself to float would drop
+                    float lg;
+                    if (A.gate == 0) lg = -softplus_f(-z) * A.gate_param;
+                    else if (A.gate == 1) lg = -A.gate_param * sigmoid_f(z);
+                    else lg = -rate * softplus_f(z);
+                    g = expm1f(lg);
                     if (FORM == 1) {
                         float ap = to_f32(((const TA*)A.a_pre)[t * A.lda + (size_t)h * dk + i]);
                         if (A.a_bias) ap += A.a_bias[(size_t)h * dk + i];
@@ -137,10 +142,10 @@ recurrence_kernel(const RecurArgs A) {
 #pragma unroll
                 for (int j = 0; j < RP / 4; ++j) {
                     const float4 qq = q4[j], kk = k4[j], gg = g4[j];
-                    s[4 * j + 0] = fmaf(gg.x, s[4 * j + 0], kk.x * vc); o = fmaf(s[4 * j + 0], qq.x, o);
-                    s[4 * j + 1] = fmaf(gg.y, s[4 * j + 1], kk.y * vc); o = fmaf(s[4 * j + 1], qq.y, o);
-                    s[4 * j + 2] = fmaf(gg.z, s[4 * j + 2], kk.z * vc); o = fmaf(s[4 * j + 2], qq.z, o);
-                    s[4 * j + 3] = fmaf(gg.w, s[4 * j + 3], kk.w * vc); o = fmaf(s[4 * j + 3], qq.w, o);
+                    s[4 * j + 0] = fmaf(gg.x, s[4 * j + 0], fmaf(kk.x, vc, s[4 * j + 0])); o = fmaf(s[4 * j + 0], qq.x, o);
+                    s[4 * j + 1] = fmaf(gg.y, s[4 * j + 1], fmaf(kk.y, vc, s[4 * j + 1])); o = fmaf(s[4 * j + 1], qq.y, o);
+                    s[4 * j + 2] = fmaf(gg.z, s[4 * j + 2], fmaf(kk.z, vc, s[4 * j + 2])); o = fmaf(s[4 * j + 2], qq.z, o);
+                    s[4 * j + 3] = fmaf(gg.w, s[4 * j + 3], fmaf(kk.w, vc, s[4 * j + 3])); o = fmaf(s[4 * j + 3], qq.w, o);
                 }
             } else if (FORM == 1) {
                 const float4* u4 = (const float4*)(us + tt * VEC + r * RPP);
@@ -157,20 +162,20 @@ recurrence_kernel(const RecurArgs A) {
 #pragma unroll
                 for (int j = 0; j < RP / 4; ++j) {
                     const float4 qq = q4[j], kk = k4[j], gg = g4[j], aa = a4[j];
-                    s[4 * j + 0] = fmaf(gg.x, s[4 * j + 0], fmaf(-aa.x, dot, kk.x * vc)); o = fmaf(s[4 * j + 0], qq.x, o);
-                    s[4 * j + 1] = fmaf(gg.y, s[4 * j + 1], fmaf(-aa.y, dot, kk.y * vc)); o = fmaf(s[4 * j + 1], qq.y, o);
-                    s[4 * j + 2] = fmaf(gg.z, s[4 * j + 2], fmaf(-aa.z, dot, kk.z * vc)); o = fmaf(s[4 * j + 2], qq.z, o);
-                    s[4 * j + 3] = fmaf(gg.w, s[4 * j + 3], fmaf(-aa.w, dot, kk.w * vc)); o = fmaf(s[4 * j + 3], qq.w, o);
+                    s[4 * j + 0] = fmaf(gg.x, s[4 * j + 0], s[4 * j + 0] + fmaf(-aa.x, dot, kk.x * vc)); o = fmaf(s[4 * j + 0], qq.x, o);
+                    s[4 * j + 1] = fmaf(gg.y, s[4 * j + 1], s[4 * j + 1] + fmaf(-aa.y, dot, kk.y * vc)); o = fmaf(s[4 * j + 1], qq.y, o);
+                    s[4 * j + 2] = fmaf(gg.z, s[4 * j + 2], s[4 * j + 2] + fmaf(-aa.z, dot, kk.z * vc)); o = fmaf(s[4 * j + 2], qq.z, o);
+                    s[4 * j + 3] = fmaf(gg.w, s[4 * j + 3], s[4 * j + 3] + fmaf(-aa.w, dot, kk.w * vc)); o = fmaf(s[4 * j + 3], qq.w, o);
                 }
             } else {
                 float dot = 0.0f;
 #pragma unroll
                 for (int j = 0; j < RP / 4; ++j) {
                     const float4 kk = k4[j], gg = g4[j];
-                    s[4 * j + 0] *= gg.x; dot = fmaf(kk.x, s[4 * j + 0], dot);
-                    s[4 * j + 1] *= gg.y; dot = fmaf(kk.y, s[4 * j + 1], dot);
-                    s[4 * j + 2] *= gg.z; dot = fmaf(kk.z, s[4 * j + 2], dot);
-                    s[4 * j + 3] *= gg.w; dot = fmaf(kk.w, s[4 * j + 3], dot);
+                    s[4 * j + 0] = fmaf(gg.x, s[4 * j + 0], s[4 * j + 0]); dot = fmaf(kk.x, s[4 * j + 0], dot);
+                    s[4 * j + 1] = fmaf(gg.y, s[4 * j + 1], s[4 * j + 1]); dot = fmaf(kk.y, s[4 * j + 1], dot);
+                    s[4 * j + 2] = fmaf(gg.z, s[4 * j + 2], s[4 * j + 2]); dot = fmaf(kk.z, s[4 * j + 2], dot);
+                    s[4 * j + 3] = fmaf(gg.w, s[4 * j + 3], s[4 * j + 3]); dot = fmaf(kk.w, s[4 * j + 3], dot);
                 }
                 dot += __shfl_xor_sync(0xffffffffu, dot, 1);
                 dot += __shfl_xor_sync(0xffffffffu, dot, 2);

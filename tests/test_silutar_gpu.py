@@ -1,0 +1,279 @@
+"""Silutar through the engine against the plain implementation (tests/plain_silutar.py), in 32-bit
+and in bfloat16, under every way of cutting the work: whole prompts, the tail token by token,
+portions down to two tokens, mixed batches over a pool so small that pages and slots are used
+again; the first tokens; long decoding across chunk and page borders; greedy generation through
+the entry point and its scheduler; the trace program."""
+from __future__ import annotations
+
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_silutar as plain
+import silutar_tiny as st
+import tiny
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"float32": 1e-4, "bfloat16": 4e-2}       # of the row's largest |logit|
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    out = {}
+    for which in st.TINY:
+        for store, dt in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+            out[(which, store)] = st.make_model_dir(str(tmp_path_factory.mktemp(f"sil{which}_{store}")), which, dt)
+    return out
+
+
+_truth = {}
+
+
+def truth(model_dir, seqs):
+    key = (model_dir, tuple((r, tuple(t)) for r, t in seqs.items()))
+    if key not in _truth:
+        cfg, w = plain.read_model(model_dir)
+        _truth[key] = {r: plain.forward(cfg, w, t) for r, t in seqs.items()}
+    return _truth[key]
+
+
+def run_steps(engine, steps, owners=None):
+    from reinfer_b200.engine import StepEntry
+    got, done = {}, {}
+    for entries, end in steps:
+        logits = engine.step([StepEntry(r, t, w) for r, t, w in entries])
+        if owners is not None:
+            owners.look()
+        row = 0
+        for r, t, w in entries:
+            base = done.get(r, 0)
+            for k in w:
+                got[(r, base + k)] = logits[row].double().cpu()
+                row += 1
+            done[r] = base + len(t)
+        for r in end:
+            engine.finish(r)
+            done.pop(r, None)
+        engine.cache.check()
+    engine.check_guards()
+    engine.check_status()
+    return got
+
+
+def compare(got, want, tol):
+    """32-bit: every row within tol of the row's largest |logit|.  bfloat16 (tol >= 1e-2): the median row within a
+    third of tol, 97 of 100 rows within tol - a read-out that happens to be near zero and is then divided by its root
+    mean square turns a rounding into a large step at that one position, whatever computes it."""
+    errs = []
+    for (r, p), row in got.items():
+        ref = want[r][p]
+        err = (row - ref).abs().max().item() / ref.abs().max().item()
+        errs.append(err)
+        if tol < 1e-2:
+            assert err <= tol, f"request {r} position {p}: error {err:.3e} of the logit scale (limit {tol})"
+    if tol >= 1e-2:
+        e = torch.tensor(errs)
+        assert e.median().item() <= tol / 3 and (e <= tol).float().mean().item() >= 0.97, \
+            f"median {e.median().item():.3e}, within tolerance {(e <= tol).float().mean().item():.3f}"
+
+
+CUTS = {"whole": tiny.cut_whole, "tail": tiny.cut_tail_one_by_one, "portions": tiny.cut_portions, "mixed": tiny.cut_mixed}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", list(st.TINY))
+@pytest.mark.parametrize("cut", list(CUTS))
+def test_cuts_match_plain(models, which, dtype, cut):
+    from reinfer_b200.engine import Engine
+    model_dir = models[(which, "f32" if dtype == "float32" else "bf16")]
+    seqs = st.sequences(which)
+    steps = CUTS[cut](seqs)
+    page = st.TINY[which][2]
+    pool = tiny.pool_tokens_needed(steps, page)                 # not a page to spare: pages are used again
+    engine = Engine.from_model_dir(model_dir, dtype=dtype, page_size=page, max_tokens=pool, max_num_seqs=4)
+    owners = tiny.PageOwners(engine.cache)
+    got = run_steps(engine, steps, owners)
+    assert len(got) == sum(len(t) for t in seqs.values())
+    compare(got, truth(model_dir, seqs), TOL[dtype])
+    assert engine.cache.free_pages() == engine.cache.total_pages() and engine.cache.free_slots() == 4
+    if cut == "mixed":
+        assert len(owners.reused) > 0
+
+
+@pytest.mark.parametrize("which", list(st.TINY))
+def test_float32_cuts_agree_bitwise(models, which):
+    """Every 32-bit kernel orders its sums by position only: all cuts give the same bits, whatever the batch, the
+    pages and the slots."""
+    from reinfer_b200.engine import Engine
+    model_dir = models[(which, "f32")]
+    seqs = st.sequences(which)
+    results = []
+    for cut in CUTS.values():
+        steps = cut(seqs)
+        page = st.TINY[which][2]
+        engine = Engine.from_model_dir(model_dir, dtype="float32", page_size=page, max_tokens=tiny.pool_tokens_needed(steps, page),
+                                       max_num_seqs=4)
+        results.append(run_steps(engine, steps))
+    for other in results[1:]:
+        for key, row in results[0].items():
+            assert torch.equal(row, other[key]), f"{key}: bits differ between cuts"
+
+
+def test_released_chunk_pages_are_reused_while_the_request_lives(models):
+    """A chunk attention layer gives pages back as soon as a chunk is over: a request four chunks long runs in a pool
+    that holds hardly more than one chunk."""
+    from reinfer_b200.engine import Engine, StepEntry
+    model_dir = models[("A", "f32")]                      # chunk of 24 positions, pages of 8
+    cfg, w = plain.read_model(model_dir)
+    seq = st.sequences("A", lengths=[100], seed=3)["r0"]
+    e = Engine.from_model_dir(model_dir, dtype="float32", page_size=8, num_pages=6, max_num_seqs=1)
+    rows, i = [], 0
+    for n in [7, 9, 2, 13, 1, 1, 1, 11, 5] + [1] * 50:
+        n = min(n, len(seq) - i)
+        if n <= 0:
+            break
+        rows.append(e.step([StepEntry("x", seq[i:i + n], list(range(n)))]))
+        i += n
+        assert e.cache.total_pages() - e.cache.free_pages() <= 5
+    assert i == len(seq)
+    got = torch.cat(rows).double().cpu()
+    ref = plain.forward(cfg, w, seq)
+    assert (got - ref).abs().max().item() <= 1e-4 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_through_captured_steps(models, dtype):
+    """Two requests decoded for hundreds of tokens across chunk edges and page borders, the decode steps replayed
+    from captured graphs; every row compared."""
+    from reinfer_b200.engine import Engine, StepEntry
+    which = "B"
+    model_dir = models[(which, "f32" if dtype == "float32" else "bf16")]
+    cfg, w = plain.read_model(model_dir)
+    seqs = st.sequences(which, lengths=[260, 190], seed=21)
+    e = Engine.from_model_dir(model_dir, dtype=dtype, page_size=16, max_tokens=512, max_num_seqs=2)
+    assert e.cuda_graphs
+    got = {}
+    e.step([StepEntry(r, t[:3], []) for r, t in seqs.items()])
+    for i in range(3, 260):
+        live = [(r, t) for r, t in seqs.items() if i < len(t)]
+        lg = e.step([StepEntry(r, [t[i]], [0]) for r, t in live])
+        for k, (r, _) in enumerate(live):
+            got[(r, i)] = lg[k].double().cpu()
+    assert e.graph_replays > 200
+    compare(got, truth(model_dir, seqs), TOL[dtype])
+
+
+def test_first_tokens_of_a_sequence(models):
+    from reinfer_b200.engine import Engine, StepEntry
+    for which in st.TINY:
+        for dtype, store in (("float32", "f32"), ("bfloat16", "bf16")):
+            model_dir = models[(which, store)]
+            cfg, w = plain.read_model(model_dir)
+            seq = [7, 3, 50, 9]
+            ref = plain.forward(cfg, w, seq)
+            e = Engine.from_model_dir(model_dir, dtype=dtype, page_size=st.TINY[which][2], max_tokens=64, max_num_seqs=2)
+            a = e.step([StepEntry("a", seq[:1], [0])])
+            b = e.step([StepEntry("b", seq, [0, 1, 2, 3]), StepEntry("a", seq[1:2], [0])])
+            c = e.step([StepEntry("a", seq[2:], [0, 1])])
+            got = torch.cat([a, b[4:5], c]).double().cpu()
+            for rows in (got, b[:4].double().cpu()):
+                if dtype == "float32":
+                    assert (rows - ref).abs().max().item() <= TOL[dtype] * ref.abs().max().item()
+                else:                                   # (a single row may sit on an ill-conditioned read-out)
+                    assert (rows - ref).abs().amax(1).median().item() <= TOL[dtype] * ref.abs().max().item()
+
+
+def test_slots_are_zeroed_when_used_again(models):
+    """A request that takes the slot of a finished one starts from an empty state and an empty convolution window."""
+    from reinfer_b200.engine import Engine, StepEntry
+    model_dir = models[("C", "f32")]
+    cfg, w = plain.read_model(model_dir)
+    seqs = st.sequences("C", lengths=[30, 22, 17], seed=5)
+    e = Engine.from_model_dir(model_dir, dtype="float32", page_size=8, max_tokens=64, max_num_seqs=1)
+    for r, t in seqs.items():
+        lg = e.step([StepEntry(r, t[:-1], []), ])
+        lg = e.step([StepEntry(r, t[-1:], [0])]).double().cpu()
+        ref = plain.forward(cfg, w, t)[-1]
+        assert (lg[0] - ref).abs().max().item() <= 1e-4 * ref.abs().max().item()
+        e.finish(r)
+
+
+def test_a_request_longer_than_the_position_table_is_refused(models):
+    from reinfer_b200.engine import Engine, StepEntry
+    from reinfer_b200.engine.engine import EngineError
+    e = Engine.from_model_dir(models[("C", "f32")], dtype="float32", page_size=8, max_tokens=512, max_num_seqs=1)
+    with pytest.raises(EngineError):
+        e.step([StepEntry("x", [1] * 257, [])])
+    assert e.cache.free_slots() == 1
+
+
+@pytest.mark.parametrize("which", ["A", "C"])
+def test_greedy_generation_through_the_entry_point(models, which):
+    """LLM.generate with its scheduler (prompts in chunks, continuous batching, three slots for five requests)
+    against the plain implementation's greedy tokens."""
+    from reinfer_b200 import LLM, SamplingParams
+    model_dir = models[(which, "f32")]
+    cfg, w = plain.read_model(model_dir)
+    seqs = st.sequences(which, lengths=[5, 17, 33, 2, 26])
+    llm = LLM(model_dir, dtype="float32", page_size=st.TINY[which][2], num_pages=64, max_num_seqs=3, max_batch_tokens=16,
+              max_chunk=7)
+    outs = llm.generate(list(seqs.values()), SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
+
+    def greedy(prompt, n):
+        toks = list(prompt)
+        for _ in range(n):
+            toks.append(int(plain.forward(cfg, w, toks)[-1].argmax()))
+        return toks[len(prompt):]
+
+    for o, p in zip(outs, seqs.values()):
+        assert o.token_ids == greedy(p, 10) and o.finish_reason == "length"
+    assert llm.engine.cache.free_pages() == 64
+
+
+def test_bfloat16_generation_follows_the_plain_logits(models):
+    from reinfer_b200 import LLM, SamplingParams
+    model_dir = models[("B", "bf16")]
+    cfg, w = plain.read_model(model_dir)
+    prompt = st.sequences("B", lengths=[24])["r0"]
+    llm = LLM(model_dir, dtype="bfloat16", page_size=16, num_pages=32, max_num_seqs=2, max_batch_tokens=64)
+    out = llm.generate(prompt, SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True))[0].token_ids
+    logits = plain.forward(cfg, w, prompt + out)
+    for i, tok in enumerate(out):
+        row = logits[len(prompt) - 1 + i]
+        assert row[tok] >= row.max() - 2 * TOL["bfloat16"] * row.abs().max() or i == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_program(models, tmp_path, dtype):
+    which = "A"
+    model_dir = models[(which, "f32" if dtype == "float32" else "bf16")]
+    seqs = st.sequences(which)
+    steps = tiny.cut_mixed(seqs, seed=11)
+    lines = [json.dumps({"step": i, "entries": [{"id": r, "tokens": t, "want": w} for r, t, w in entries], "end": end})
+             for i, (entries, end) in enumerate(steps)]
+    out = tmp_path / "out"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
+                        "--out", str(out), "--max-tokens", str(tiny.pool_tokens_needed(steps))],
+                       input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(len(steps))]
+    want = truth(model_dir, seqs)
+    vocab = st.TINY[which][0]["vocab"]
+    done, got = {}, {}
+    for i, (entries, end) in enumerate(steps):
+        arr = np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, vocab)
+        row = 0
+        for r, t, w in entries:
+            for k in w:
+                got[(r, done.get(r, 0) + k)] = torch.from_numpy(arr[row].astype(np.float64))
+                row += 1
+            done[r] = done.get(r, 0) + len(t)
+        assert row == arr.shape[0]
+    compare(got, want, TOL[dtype])
