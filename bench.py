@@ -80,6 +80,39 @@ REFERENCE_UNAVAILABLE = ("the reference is a Rust workspace (no Python package, 
                          "pip cannot install it offline")
 
 
+DESIGN_SIZES = {"w2048": dict(width=2048, heads=16, ff=8192, layers=6), "w4096": dict(width=4096, heads=32, ff=12288, layers=3)}
+
+
+def design_run(a, measure) -> int:
+    """--design silutar: the new design and the closest existing one (Qwen3) at equal layer sizes, bf16 random weights:
+    prefill of 2,048 tokens and decode at --batch requests of 2,048 tokens, device time by CUDA events, and one eager
+    step of each kind by kernel family with each family's share of the measured peaks."""
+    hbm_gbs, tf_burst, _, peak_src = measure.peaks(ROOT)
+    clocks = ClockSampler()
+    clocks.start()
+    sizes = {}
+    for name, sz in DESIGN_SIZES.items():
+        row = {}
+        for design, make in (("silutar", measure.silutar_shape), ("qwen3", measure.qwen3_shape)):
+            r = measure.time_design(make(**sz), prompt=2048, batch=a.batch, context=2048, steps=max(8, a.steps // 2),
+                                    page_size=a.page_size, segments=not a.no_segments)
+            for kind in ("decode", "prefill"):
+                seg = r.pop(kind + "_segments", None)
+                if seg:
+                    print(f"-- {design} {name}: one eager {kind} step by kernel family --", file=sys.stderr)
+                    print("\n".join(measure.segment_table(seg, hbm_gbs, tf_burst)), file=sys.stderr)
+                    r[kind + "_families"] = {k: [round(d["us"], 1), d["n"], round(100 * max(d["tflops"] / tf_burst, d["gbs"] / hbm_gbs), 1)]
+                                             for k, d in sorted(seg.items(), key=lambda kv: -kv[1]["us"])[:8]}
+            row[design] = r
+        sizes[name] = dict(sz, **row)
+    clk = clocks.finish()
+    print(json.dumps({"metric": "prefill and decode tok/s of the Silutar design beside Qwen3 at equal layer sizes", "unit": "tokens/s",
+                      "n_gpus": 1, "dtype": "bf16", "data": "synthetic: random weights, uniform-random token ids",
+                      "batch": a.batch, "prompt": 2048, "context": 2048, "families": "[us, launches, % of the measured peak]",
+                      "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": tf_burst, "source": peak_src}, "sizes": sizes, "clocks": clk}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -93,6 +126,9 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page")
     ap.add_argument("--no-segments", action="store_true")
+    ap.add_argument("--design", default=None, choices=["silutar"],
+                    help="instead of the default workload: prefill and decode of this design at a few layer sizes, beside "
+                         "Qwen3 at equal sizes (random weights); prints one JSON line of its own")
     a = ap.parse_args()
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
@@ -104,6 +140,9 @@ def main() -> int:
 
     import torch
     from reinfer_b200 import measure, ops
+
+    if a.design == "silutar":
+        return design_run(a, measure)
 
     shape = a.shape.lower()
     big = shape.endswith("32b")

@@ -17,6 +17,11 @@
 //    runs one CTA per query head over the whole context and re-reads K/V per head,
 //    crates/cuda/kernels/decode_flash_kernels.cu:167-369.)
 //
+// Two optional extras serve attention that is local to chunks of positions and has no rotation: a chunk mask (a row
+// sees only the keys from the start of its own chunk of `chunk` positions, counted from position 0) and a penalty on
+// distance per query head, score -= r1[h] ln(1 + r2[h] (i - j)), added in the exponent's base-2 domain as
+// r1 log2(1 + r2 (i - j)); and a factor on the output.  Without them the kernels are what they were.
+//
 // Head sizes: the template is instantiated for 32, 64, 128 and 256; a head size that is a
 // multiple of 8 below the next instance is zero-padded in shared memory.
 #include "common.cuh"
@@ -41,6 +46,10 @@ struct FaArgs {
     int first_entry, n_entries;        // entries this launch covers: [first_entry, first_entry + n_entries)
     int n_splits;
     float scale_log2;
+    int chunk;                         // > 0: keys before floor(pos / chunk) * chunk are not seen
+    const float* r1;                   // [QH] distance penalty (null: none)
+    const float* r2;
+    float out_scale;
 };
 
 // ---------------------------------------------------------------- small PTX wrappers
@@ -118,7 +127,8 @@ __device__ __forceinline__ void fa_load_tile(unsigned char* stage, const FaArgs&
 template <int D, int NT>
 __device__ __forceinline__ void fa_tile(const unsigned char* sQ, const unsigned char* sK, const unsigned char* sV,
                                         int koff, int k0_abs, int pos0, int pos1, int lo0, int lo1, float scale_log2,
-                                        float (&o)[D / 8][4], float (&m)[2], float (&l)[2]) {
+                                        float (&o)[D / 8][4], float (&m)[2], float (&l)[2],
+                                        bool pen = false, float pa0 = 0.0f, float pb0 = 0.0f, float pa1 = 0.0f, float pb1 = 0.0f) {
     constexpr int STRIDE = FaSmem<D>::STRIDE;
     const int lane = threadIdx.x & 31;
     float s[NT][4];
@@ -141,10 +151,17 @@ __device__ __forceinline__ void fa_tile(const unsigned char* sQ, const unsigned 
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
         const int key = k0_abs + koff + j * 8 + 2 * (lane & 3);
-        s[j][0] = (key >= lo0 && key <= pos0) ? s[j][0] * scale_log2 : -INFINITY;
-        s[j][1] = (key + 1 >= lo0 && key + 1 <= pos0) ? s[j][1] * scale_log2 : -INFINITY;
-        s[j][2] = (key >= lo1 && key <= pos1) ? s[j][2] * scale_log2 : -INFINITY;
-        s[j][3] = (key + 1 >= lo1 && key + 1 <= pos1) ? s[j][3] * scale_log2 : -INFINITY;
+        float v0 = s[j][0] * scale_log2, v1 = s[j][1] * scale_log2, v2 = s[j][2] * scale_log2, v3 = s[j][3] * scale_log2;
+        if (pen) {                                             // the distance penalty (masked places are replaced below)
+            v0 = fmaf(-pa0, __log2f(fmaf(pb0, (float)(pos0 - key), 1.0f)), v0);
+            v1 = fmaf(-pa0, __log2f(fmaf(pb0, (float)(pos0 - key - 1), 1.0f)), v1);
+            v2 = fmaf(-pa1, __log2f(fmaf(pb1, (float)(pos1 - key), 1.0f)), v2);
+            v3 = fmaf(-pa1, __log2f(fmaf(pb1, (float)(pos1 - key - 1), 1.0f)), v3);
+        }
+        s[j][0] = (key >= lo0 && key <= pos0) ? v0 : -INFINITY;
+        s[j][1] = (key + 1 >= lo0 && key + 1 <= pos0) ? v1 : -INFINITY;
+        s[j][2] = (key >= lo1 && key <= pos1) ? v2 : -INFINITY;
+        s[j][3] = (key + 1 >= lo1 && key + 1 <= pos1) ? v3 : -INFINITY;
         mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
         mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
     }
@@ -226,14 +243,19 @@ fa_prefill_kernel(const FaArgs a) {
 
     fa_load_q<D>(sQ, a, a.cu_q[e] + q0, n_tok, head0, FA_BM);
     const int pos_min = start_pos + q0, pos_max = start_pos + q0 + n_tok - 1;
-    const int lo_min = a.window > 0 ? max(0, pos_min - a.window + 1) : 0;
+    int lo_min = a.window > 0 ? max(0, pos_min - a.window + 1) : 0;
+    if (a.chunk > 0) lo_min = max(lo_min, pos_min / a.chunk * a.chunk);
     const int t_begin = lo_min / FA_BN, t_end = pos_max / FA_BN + 1;
 
     // this thread's two rows
     const int r0 = warp * 16 + (lane >> 2), r1 = r0 + 8;
     const int ti0 = r0 / a.Gc, ti1 = r1 / a.Gc;
     const int pos0 = ti0 < n_tok ? start_pos + q0 + ti0 : -1, pos1 = ti1 < n_tok ? start_pos + q0 + ti1 : -1;
-    const int lo0 = a.window > 0 ? max(0, pos0 - a.window + 1) : 0, lo1 = a.window > 0 ? max(0, pos1 - a.window + 1) : 0;
+    int lo0 = a.window > 0 ? max(0, pos0 - a.window + 1) : 0, lo1 = a.window > 0 ? max(0, pos1 - a.window + 1) : 0;
+    if (a.chunk > 0) { lo0 = max(lo0, max(pos0, 0) / a.chunk * a.chunk); lo1 = max(lo1, max(pos1, 0) / a.chunk * a.chunk); }
+    const bool pen = a.r1 != nullptr;
+    const int hd0 = head0 + r0 % a.Gc, hd1 = head0 + r1 % a.Gc;
+    const float pa0 = pen ? a.r1[hd0] : 0.0f, pb0 = pen ? a.r2[hd0] : 0.0f, pa1 = pen ? a.r1[hd1] : 0.0f, pb1 = pen ? a.r2[hd1] : 0.0f;
     // keys beyond the last row of this WARP are masked for all its rows: the warp may stop early
     const int warp_last_tok = min(n_tok - 1, (warp * 16 + 15) / a.Gc);
     const int warp_t_end = (warp * 16) / a.Gc < n_tok ? (start_pos + q0 + warp_last_tok) / FA_BN + 1 : 0;
@@ -254,7 +276,7 @@ fa_prefill_kernel(const FaArgs a) {
         if (t < warp_t_end) {
             const unsigned char* sK = stages + buf * FaSmem<D>::STAGE;
             fa_tile<D, FA_BN / 8>(sQ + warp * 16 * FaSmem<D>::STRIDE, sK, sK + FaSmem<D>::TILE, 0, t * FA_BN,
-                                  pos0, pos1, lo0, lo1, a.scale_log2, o, m, l);
+                                  pos0, pos1, lo0, lo1, a.scale_log2, o, m, l, pen, pa0, pb0, pa1, pb1);
         }
     }
     cp_async_wait<0>();
@@ -264,7 +286,7 @@ fa_prefill_kernel(const FaArgs a) {
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
     }
-    const float inv0 = l[0] > 0.0f ? 1.0f / l[0] : 0.0f, inv1 = l[1] > 0.0f ? 1.0f / l[1] : 0.0f;
+    const float inv0 = l[0] > 0.0f ? a.out_scale / l[0] : 0.0f, inv1 = l[1] > 0.0f ? a.out_scale / l[1] : 0.0f;
     const int tok_base = a.cu_q[e] + q0;
 #pragma unroll
     for (int j = 0; j < D / 8; ++j) {
@@ -292,7 +314,8 @@ fa_decode_kernel(const FaArgs a) {
     const int split = blockIdx.z;
     const int kv_end = a.kv_len[e];
     const int pos = kv_end - 1;
-    const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    if (a.chunk > 0) lo = max(lo, max(pos, 0) / a.chunk * a.chunk);
     const int tok = a.cu_q[e];
     const int* bt = a.block_table + (size_t)e * a.max_pages;
     const int t_lo = lo / FA_BN, t_hi = pos / FA_BN + 1;
@@ -302,6 +325,9 @@ fa_decode_kernel(const FaArgs a) {
     fa_load_q<D>(sQ, a, tok, 1, head0, 16);
     const int row0 = lane >> 2;                                // rows >= Gc are padding
     const int pos0 = row0 < a.Gc ? pos : -1, pos1 = row0 + 8 < a.Gc ? pos : -1;
+    const bool pen = a.r1 != nullptr;
+    const float pa0 = (pen && row0 < a.Gc) ? a.r1[head0 + row0] : 0.0f, pb0 = (pen && row0 < a.Gc) ? a.r2[head0 + row0] : 0.0f;
+    const float pa1 = (pen && row0 + 8 < a.Gc) ? a.r1[head0 + row0 + 8] : 0.0f, pb1 = (pen && row0 + 8 < a.Gc) ? a.r2[head0 + row0 + 8] : 0.0f;
     float o[D / 8][4];
 #pragma unroll
     for (int j = 0; j < D / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f; }
@@ -320,7 +346,7 @@ fa_decode_kernel(const FaArgs a) {
             fa_load_tile<D>(stages + ((it + NST - 1) % NST) * FaSmem<D>::STAGE, a, bt, kh, (t + NST - 1) * FA_BN, kv_end);
         cp_async_commit();
         const unsigned char* sK = stages + (it % NST) * FaSmem<D>::STAGE;
-        fa_tile<D, 2>(sQ, sK, sK + FaSmem<D>::TILE, warp * 16, t * FA_BN, pos0, pos1, lo, lo, a.scale_log2, o, m, l);
+        fa_tile<D, 2>(sQ, sK, sK + FaSmem<D>::TILE, warp * 16, t * FA_BN, pos0, pos1, lo, lo, a.scale_log2, o, m, l, pen, pa0, pb0, pa1, pb1);
     }
     cp_async_wait<0>();
     __syncthreads();                                           // the stages are free: reuse them for the merge
@@ -357,7 +383,7 @@ fa_decode_kernel(const FaArgs a) {
                 O += sO[(w * 16 + row) * D + dim] * f;
             }
         }
-        const float val = L > 0.0f ? O / L : 0.0f;
+        const float val = L > 0.0f ? O / L * a.out_scale : 0.0f;
         const int head = head0 + row;
         if (a.n_splits == 1) {
             a.out[((size_t)tok * a.QH + head) * a.d + dim] = __float2bfloat16_rn(val);
@@ -438,10 +464,13 @@ extern "C" int rb_fa_group_chunk(int G) { return fa_group_chunk(G); }
 
 extern "C" int rb_fa_prefill(const void* q, const void* cache, const int* block_table, const int* cu_q, const int* kv_len,
                              void* out, int first_entry, int n_entries, int n_tiles, int QH, int KH, int d, int page_size,
-                             int max_pages, int window, float scale, void* stream) {
+                             int max_pages, int window, float scale, int chunk, const float* r1, const float* r2, float out_scale,
+                             void* stream) {
     if (n_entries <= 0 || n_tiles <= 0) return 0;
     if (fa_check(QH, KH, d, page_size, max_pages)) return -1;
+    if (chunk < 0 || (r1 == nullptr) != (r2 == nullptr)) RB_REFUSE("attention: chunk %d, or half a distance penalty", chunk);
     FaArgs a{};
+    a.chunk = chunk; a.r1 = r1; a.r2 = r2; a.out_scale = out_scale;
     a.q = (const bf16*)q; a.cache = (const bf16*)cache; a.block_table = block_table; a.cu_q = cu_q; a.kv_len = kv_len;
     a.out = (bf16*)out; a.QH = QH; a.KH = KH; a.d = d; a.page_size = page_size; a.page_shift = fa_shift(page_size); a.max_pages = max_pages; a.window = window;
     a.Gc = fa_group_chunk(QH / KH); a.chunks = (QH / KH) / a.Gc; a.first_entry = first_entry; a.n_entries = n_entries;
@@ -458,14 +487,16 @@ extern "C" int rb_fa_prefill(const void* q, const void* cache, const int* block_
 extern "C" int rb_fa_decode(const void* q, const void* cache, const int* block_table, const int* cu_q, const int* kv_len,
                             void* out, float* part_o, float* part_lse, int first_entry, int n_entries, int first_tok,
                             int n_splits, int QH, int KH, int d, int page_size, int max_pages, int window, float scale,
-                            void* stream) {
+                            int chunk, const float* r1, const float* r2, float out_scale, void* stream) {
     if (n_entries <= 0) return 0;
     if (fa_check(QH, KH, d, page_size, max_pages)) return -1;
+    if (chunk < 0 || (r1 == nullptr) != (r2 == nullptr)) RB_REFUSE("attention: chunk %d, or half a distance penalty", chunk);
     if (n_splits < 1 || n_splits > 65535) RB_REFUSE("attention: %d splits", n_splits);
     if (n_splits > 1 && (!part_o || !part_lse)) RB_REFUSE("attention: split decoding needs its scratch");
     FaArgs a{};
     a.q = (const bf16*)q; a.cache = (const bf16*)cache; a.block_table = block_table; a.cu_q = cu_q; a.kv_len = kv_len;
     a.out = (bf16*)out; a.part_o = part_o; a.part_lse = part_lse;
+    a.chunk = chunk; a.r1 = r1; a.r2 = r2; a.out_scale = out_scale;
     a.QH = QH; a.KH = KH; a.d = d; a.page_size = page_size; a.page_shift = fa_shift(page_size); a.max_pages = max_pages; a.window = window;
     a.Gc = fa_group_chunk(QH / KH); a.chunks = (QH / KH) / a.Gc; a.first_entry = first_entry; a.n_entries = n_entries;
     a.n_splits = n_splits; a.scale_log2 = scale * 1.4426950408889634f;

@@ -290,3 +290,108 @@ def compact_segments(seg: Dict, top: int = 6) -> Dict:
     """The `top` segments by time as {name: [us, TFLOP/s, GB/s]} for a one-line record."""
     keep = sorted(seg.items(), key=lambda kv: -kv[1]["us"])[:top]
     return {k: [round(d["us"], 1), round(d["tflops"], 1), round(d["gbs"])] for k, d in keep}
+
+
+# ------------------------------------------------------------------ two designs side by side
+def silutar_shape(width: int, heads: int, ff: int, layers: int, vocab: int = 32768, chunk: int = 1024, head_dim: int = 128,
+                  kv_heads: int = 0, positions: int = 8192) -> Dict:
+    """A Silutar config.json at layer sizes that resemble a real model's: `layers` layers that cycle through the
+    three mixers (parallel, channel_delta, gla), heads of `head_dim`, low-rank maps of width / 16."""
+    kv = kv_heads or max(1, heads // 4)
+    rank = max(16, width // 16)
+    mixers = [
+        {"type": "parallel", "mixer": {"left": {"heads": heads, "kv_heads": kv, "dim": head_dim, "vdim": head_dim, "conv": 4,
+                                                "mask": {"size": chunk}, "scale": head_dim ** -0.5},
+                                       "right": {"heads": heads, "dim": head_dim // 2, "decay_rank": rank},
+                                       "left_scale": 0.5, "right_scale": 0.5}},
+        {"type": "channel_delta", "mixer": {"heads": heads, "kv_heads": kv, "dim": head_dim, "vdim": head_dim, "conv": 4,
+                                            "decay_rank": rank, "gate_rank": rank}},
+        {"type": "gla", "mixer": {"heads": heads, "dim": head_dim // 2, "vdim": head_dim, "tau": 16.0, "decay_rank": rank}},
+    ]
+    return {"architecture": "Silutar", "vocab": vocab, "width": width, "max_positions": positions, "norm": {"eps": 1e-6},
+            "logit_softcap": 30.0,
+            "layers": [dict(mixers[i % 3], mlp={"kind": "dense", "ff": ff}) for i in range(layers)]}
+
+
+def qwen3_shape(width: int, heads: int, ff: int, layers: int, vocab: int = 32768, head_dim: int = 128, kv_heads: int = 0,
+                positions: int = 8192) -> Dict:
+    """The closest existing design at the same layer sizes."""
+    return {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "head_dim": head_dim, "vocab_size": vocab,
+            "rope_theta": 1e6, "rms_norm_eps": 1e-6, "max_position_embeddings": positions, "num_hidden_layers": layers,
+            "hidden_size": width, "num_attention_heads": heads, "num_key_value_heads": kv_heads or max(1, heads // 4),
+            "intermediate_size": ff, "tie_word_embeddings": True}
+
+
+def time_design(raw: Dict, prompt: int = 2048, batch: int = 8, context: int = 2048, steps: int = 32, page_size: int = 16,
+                seed: int = 0, segments: bool = True) -> Dict:
+    """Random weights of the configuration `raw` on the device; prefill of one `prompt`-token request and decode steps
+    of `batch` requests at `context` tokens, both timed on the device by CUDA events (decode: replays of the captured
+    step); and one eager step of each kind by kernel family."""
+    import torch
+    from . import ops
+    from .config.registry import resolve_architecture
+    from .engine import Engine, StepEntry
+    cfg = resolve_architecture(raw).config_cls.from_dict(raw)
+    pool = batch * (context + 2 * page_size) + 2 * prompt
+    engine = Engine.from_config(cfg, seed=seed, dtype="bfloat16", page_size=page_size, max_tokens=pool, max_num_seqs=batch + 2)
+    gen = torch.Generator().manual_seed(seed)
+    toks = lambda n: torch.randint(0, engine.vocab_size, (n,), generator=gen).tolist()
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    out: Dict = {}
+    ms = []
+    for _ in range(4):
+        e0, e1 = ev(), ev()
+        t = toks(prompt)
+        torch.cuda.synchronize()
+        e0.record()
+        engine.step([StepEntry("p", t, [prompt - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        ms.append(e0.elapsed_time(e1))
+        engine.finish("p")
+    out["prefill_ms"] = min(ms[1:])
+    out["prefill_tok_s"] = prompt / out["prefill_ms"] * 1e3
+    for b in range(batch):
+        t = toks(context - steps - 8)
+        for i in range(0, len(t), 2048):
+            engine.step([StepEntry(("d", b), t[i:i + 2048], [])])
+    for _ in range(4):
+        engine.step([StepEntry(("d", b), [3 + b], [0]) for b in range(batch)])
+    graph = next(iter(engine._graphs.values())) if engine._graphs else None
+    torch.cuda.synchronize()
+    e0, e1 = ev(), ev()
+    e0.record()
+    for _ in range(steps):
+        if graph is not None:
+            graph.graph.replay()        # the same tokens at the same places again: the step's work is what is timed
+        else:
+            engine.step([StepEntry(("d", b), [3 + b], [0]) for b in range(batch)])
+    e1.record()
+    torch.cuda.synchronize()
+    out["decode_ms"] = e0.elapsed_time(e1) / steps
+    out["decode_tok_s"] = batch / out["decode_ms"] * 1e3
+    out["decode_launches"] = graph.n_launches if graph is not None else None
+    out["captured"] = graph is not None
+    if segments:
+        was, engine.cuda_graphs = engine.cuda_graphs, False
+        try:
+            for kind, entries in (("decode", [StepEntry(("d", b), [9 + b], [0]) for b in range(batch)]),
+                                  ("prefill", [StepEntry("s", toks(prompt), [prompt - 1])])):
+                prof = ops.SegmentProfiler()
+                torch.cuda.synchronize()
+                torch.cuda._sleep(40_000_000)
+                old = ops.set_profiler(prof)
+                prof.begin()
+                try:
+                    engine.step(entries)
+                finally:
+                    ops.set_profiler(old)
+                out[kind + "_segments"] = prof.summary()
+        finally:
+            engine.cuda_graphs = was
+    status = ops.status_word()
+    if status:
+        raise RuntimeError(f"kernel status word 0x{status:x}")
+    del engine
+    torch.cuda.empty_cache()
+    return out

@@ -319,9 +319,20 @@ def fa_group_chunk(group: int) -> int:
     return 1
 
 
+def _penalty_args(penalty, QH: int):
+    if penalty is None:
+        return c_void_p(0), c_void_p(0)
+    r1, r2 = penalty
+    _need(r1.dtype == torch.float32 and r2.dtype == torch.float32 and r1.numel() == QH and r2.numel() == QH,
+          "attention: the distance penalty is two float32 vectors, one number per query head each")
+    return _p(r1), _p(r2)
+
+
 def fa_decode(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, first_tok: int, n_splits: int,
-              QH: int, KH: int, d: int, page_size: int, window: int, scale: float, work=(0.0, 0.0)) -> None:
-    """Split-K flash decoding (tensor cores) for entries that bring one token each."""
+              QH: int, KH: int, d: int, page_size: int, window: int, scale: float, work=(0.0, 0.0),
+              chunk: int = 0, penalty=None, out_scale: float = 1.0) -> None:
+    """Split-K flash decoding (tensor cores) for entries that bring one token each.  chunk, penalty = (r1, r2) and
+    out_scale as in paged_attention_ref."""
     part_o = part_lse = None
     if n_splits > 1:
         part_o = torch.empty(n_entries * QH * n_splits * d, dtype=torch.float32, device=q.device)
@@ -329,7 +340,7 @@ def fa_decode(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entr
     _check(lib().rb_fa_decode(_p(q), _p(cache), _p(block_table), _p(cu_q), _p(kv_len), _p(out), _p(part_o), _p(part_lse),
                               c_int(first_entry), c_int(n_entries), c_int(first_tok), c_int(n_splits), c_int(QH), c_int(KH),
                               c_int(d), c_int(page_size), c_int(block_table.shape[1]), c_int(window), c_float(scale),
-                              _stream()), "fa_decode", *work)
+                              c_int(chunk), *_penalty_args(penalty, QH), c_float(out_scale), _stream()), "fa_decode", *work)
     if n_splits > 1:
         global launches
         launches += 1                      # the merge kernel
@@ -479,11 +490,14 @@ def tma_pages(page_size: int) -> bool:
 
 
 def fa_prefill(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, n_tiles: int,
-               QH: int, KH: int, d: int, page_size: int, window: int, scale: float, work=(0.0, 0.0)) -> None:
-    """Paged causal flash attention (tensor cores) for entries that bring several tokens."""
+               QH: int, KH: int, d: int, page_size: int, window: int, scale: float, work=(0.0, 0.0),
+               chunk: int = 0, penalty=None, out_scale: float = 1.0) -> None:
+    """Paged causal flash attention (tensor cores) for entries that bring several tokens.  chunk, penalty = (r1, r2)
+    and out_scale as in paged_attention_ref."""
     _check(lib().rb_fa_prefill(_p(q), _p(cache), _p(block_table), _p(cu_q), _p(kv_len), _p(out), c_int(first_entry),
                                c_int(n_entries), c_int(n_tiles), c_int(QH), c_int(KH), c_int(d), c_int(page_size),
-                               c_int(block_table.shape[1]), c_int(window), c_float(scale), _stream()), "fa_prefill", *work)
+                               c_int(block_table.shape[1]), c_int(window), c_float(scale), c_int(chunk),
+                               *_penalty_args(penalty, QH), c_float(out_scale), _stream()), "fa_prefill", *work)
 
 
 USE_TMA_ATTENTION = os.environ.get("REINFER_B200_TMA_ATTENTION", "1") != "0"
@@ -922,8 +936,38 @@ def chunk_attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch
                     chunk: int, scale: float, penalty, out_scale: float = 1.0) -> None:
     """Attention of a step's tokens over the keys of their own chunk, with the logarithmic distance penalty
     (parts/chunk_attention.py).  q [T, QH, dk], out [T, QH, dv]."""
-    paged_attention_ref(q, cache, group.block_table, ctx.tok_entry, ctx.positions, out, QH, KH, dk, group.page_size, 0, scale,
-                        dv=dv, chunk=chunk, penalty=penalty, out_scale=out_scale)
+    n_dec, E = ctx.n_decode, ctx.n_entries
+    dec_work = pre_work = (0.0, 0.0)
+    if _profiler is not None:
+        def work(first, last):
+            """(flops, bytes) of entries first..last-1: two products per (query head, visible key) pair, the keys and
+            values of the chunks the portion touches read once."""
+            pairs = keys = toks = 0.0
+            for e in range(first, last):
+                n, s0 = ctx.q_start[e + 1] - ctx.q_start[e], ctx.start_pos[e]
+                pairs += sum((p % chunk) + 1 for p in range(s0, s0 + n)) if n <= 4096 else n * (chunk + 1) / 2
+                keys += (s0 + n) - (s0 // chunk * chunk)
+                toks += n
+            return 2.0 * QH * (dk + dv) * pairs, (keys * KH * (dk + dv) + toks * QH * (dk + dv)) * q.element_size()
+        dec_work, pre_work = work(0, n_dec), work(n_dec, E)
+    if q.dtype != torch.bfloat16 or dk != dv or dk % 8 or dk > 256:
+        # 32-bit, or value heads of their own size: the plain kernel
+        paged_attention_ref(q, cache, group.block_table, ctx.tok_entry, ctx.positions, out, QH, KH, dk, group.page_size, 0, scale,
+                            work=(dec_work[0] + pre_work[0], dec_work[1] + pre_work[1]), dv=dv, chunk=chunk, penalty=penalty,
+                            out_scale=out_scale)
+        return
+    gc = fa_group_chunk(QH // KH)
+    if n_dec:
+        # a token's keys are those of its chunk: at most chunk / 64 tiles; they are split over CTAs while that fills the device
+        ctas = n_dec * KH * (QH // KH // gc)
+        n_splits = max(1, min(DECODE_SLOTS // max(ctas, 1), -(-chunk // 256), 16))
+        fa_decode(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, 0, n_dec, 0, n_splits, QH, KH, dk, group.page_size, 0,
+                  scale, work=dec_work, chunk=chunk, penalty=penalty, out_scale=out_scale)
+    if E > n_dec:
+        tpt = 64 // gc
+        n_tiles = sum(-(-(ctx.q_start[e + 1] - ctx.q_start[e]) // tpt) for e in range(n_dec, E))
+        fa_prefill(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, n_dec, E - n_dec, n_tiles, QH, KH, dk, group.page_size,
+                   0, scale, work=pre_work, chunk=chunk, penalty=penalty, out_scale=out_scale)
 
 
 RECURRENCE_FORMS = {"diagonal": 0, "delta_old_state": 1, "delta_gated_state": 2}
@@ -935,10 +979,11 @@ def recurrence(form: str, gate: str, q: torch.Tensor, k: torch.Tensor, v: torch.
                entry_slot: torch.Tensor, n_entries: int, H: int, Hk: int, dk: int, dv: int, *, gate_param: float = 0.0,
                q_scale: float = 1.0, unit_qk: bool = False, a_pre: Optional[torch.Tensor] = None,
                a_bias: Optional[torch.Tensor] = None, b_pre: Optional[torch.Tensor] = None,
-               rate: Optional[torch.Tensor] = None) -> None:
+               rate: Optional[torch.Tensor] = None, max_q_len: int = 1 << 30) -> None:
     """The token-by-token recurrence over state [slots, H, dk, dv] (float32) of csrc/recurrence.cu.  q, k [T, Hk*dk],
     v [T, H*dv], a_pre [T, H*dk], b_pre [T, H] in the activation dtype (rows may be strided); z [T, H*dk] float32;
-    z_bias, a_bias [H*dk] and rate [H] float32; out [T, H, dv] float32."""
+    z_bias, a_bias [H*dk] and rate [H] float32; out [T, H, dv] float32.  max_q_len: the step's longest portion (the
+    default says "unknown: may be long")."""
     _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, dk, dv),
           "recurrence: state float32 [slots, H, dk, dv]")
     _need(out.dtype == torch.float32 and out.is_contiguous() and z.dtype == torch.float32, "recurrence: out and z float32")
@@ -949,13 +994,22 @@ def recurrence(form: str, gate: str, q: torch.Tensor, k: torch.Tensor, v: torch.
         _need(t is None or (t.dtype == torch.float32 and t.is_contiguous()), "recurrence: small vectors float32")
     ld = lambda t: c_longlong(t.stride(0) if t is not None else 0)
     T = q.shape[0]
+    # a step with a portion longer than one tile has its gates and unit vectors prepared ahead, in parallel over the
+    # step's tokens, into a scratch buffer (a decode step, whose captured form has max_q_len 1, never takes it)
+    prep = None
+    if max_q_len > int(lib().rb_recurrence_tile(c_int(dk))):
+        prep = torch.empty(T * H * int(lib().rb_recurrence_record_floats(c_int(RECURRENCE_FORMS[form]), c_int(dk), c_int(dv))),
+                           dtype=torch.float32, device=q.device)
     _check(lib().rb_recurrence(c_int(RECURRENCE_FORMS[form]), c_int(RECURRENCE_GATES[gate]), c_int(dt(q)),
                                _p(q), ld(q), _p(k), ld(k), _p(v), ld(v), _p(z), ld(z), _p(z_bias),
                                _p(a_pre), ld(a_pre), _p(a_bias), _p(b_pre), ld(b_pre), _p(rate),
                                c_float(gate_param), c_float(q_scale), c_int(int(unit_qk)),
                                _p(state), _p(out), _p(cu_q), _p(entry_slot), c_int(n_entries), c_int(H), c_int(Hk),
-                               c_int(dk), c_int(dv), _stream()), f"recurrence {form}",
+                               c_int(dk), c_int(dv), _p(prep), c_int(T), c_int(max_q_len), _stream()), f"recurrence {form}",
            6.0 * T * H * dk * dv, float(T * H * (2 * dk + 2 * dv) * 4 + 2 * n_entries * H * dk * dv * 4))
+    if prep is not None:
+        global launches
+        launches += 1                      # the preparation kernel
 
 
 def random_normal(out: torch.Tensor, base: int, mean: float, std: float) -> None:

@@ -94,7 +94,7 @@ class GatedLinearAttention(_RecurrentMixer):
         o = torch.empty((T, H, dv), dtype=torch.float32, device=proj.device)
         ops.recurrence("diagonal", "sigmoid_root", self._col(proj, "q"), self._col(proj, "k"), self._col(proj, "v"),
                        z, self.a2_bias, cache.state, o, ctx.cu_q, ctx.entry_slot, ctx.n_entries, H, H, dk, dv,
-                       gate_param=1.0 / self.tau, q_scale=dk ** -0.5)
+                       gate_param=1.0 / self.tau, q_scale=dk ** -0.5, max_q_len=ctx.max_q_len)
         y = torch.empty((T, H * dv), dtype=proj.dtype, device=proj.device)
         ops.head_norm_gate(o, self.norm_w, self._col(proj, "g"), y, H, dv, self.eps, "silu", self.out_scale)
         return matmul_into_residual(ctx, y, self.w_o, residual)
@@ -131,7 +131,7 @@ class GeneralDeltaRule(_RecurrentMixer):
         o = torch.empty((T, H, d), dtype=torch.float32, device=proj.device)
         ops.recurrence("delta_old_state", "exp_sigmoid", self._col(proj, "r"), self._col(proj, "k"), self._col(proj, "v"),
                        z, self.w0, cache.state, o, ctx.cu_q, ctx.entry_slot, ctx.n_entries, H, H, d, d,
-                       gate_param=self.DECAY_SCALE, a_pre=self._col(proj, "a"), a_bias=self.a_bias)
+                       gate_param=self.DECAY_SCALE, a_pre=self._col(proj, "a"), a_bias=self.a_bias, max_q_len=ctx.max_q_len)
         y = torch.empty((T, H * d), dtype=proj.dtype, device=proj.device)
         ops.head_norm_gate(o, self.norm_w, self._col(proj, "g"), y, H, d, self.eps, "sigmoid", self.out_scale)
         return matmul_into_residual(ctx, y, self.w_o, residual)
@@ -175,7 +175,7 @@ class ChannelGatedDeltaRule(_RecurrentMixer):
         o = torch.empty((T, H, dv), dtype=torch.float32, device=proj.device)
         ops.recurrence("delta_gated_state", "exp_softplus", y[:, :G * dk], y[:, G * dk:2 * G * dk], y[:, 2 * G * dk:],
                        z, self.dt_bias, cache.state["S"], o, ctx.cu_q, ctx.entry_slot, ctx.n_entries, H, G, dk, dv,
-                       q_scale=dk ** -0.5, unit_qk=True, b_pre=self._col(proj, "b"), rate=self.a_log)
+                       q_scale=dk ** -0.5, unit_qk=True, b_pre=self._col(proj, "b"), rate=self.a_log, max_q_len=ctx.max_q_len)
         out = torch.empty((T, H * dv), dtype=proj.dtype, device=proj.device)
         ops.head_norm_gate(o, self.norm_w, gate, out, H, dv, self.eps, "sigmoid", self.out_scale)
         return matmul_into_residual(ctx, out, self.w_o, residual)

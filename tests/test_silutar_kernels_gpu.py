@@ -288,7 +288,7 @@ def test_chunk_attention_sees_its_chunk_and_nothing_else(dtype, QH, KH, dk, dv, 
         T = hi - lo
         ctx = SimpleNamespace(tok_entry=torch.zeros(T, dtype=torch.int32, device=DEV),
                               positions=torch.arange(lo, hi, dtype=torch.int32, device=DEV),
-                              n_decode=0, n_entries=1, q_start=[0, T], start_pos=[lo], max_kv_len=hi, decode_kv_tiles=None,
+                              n_decode=1 if T == 1 else 0, n_entries=1, q_start=[0, T], start_pos=[lo], max_kv_len=hi, decode_kv_tiles=None,
                               cu_q=torch.tensor([0, T], dtype=torch.int32, device=DEV),
                               kv_len=torch.tensor([hi], dtype=torch.int32, device=DEV))
         out = torch.empty(T, QH, dv, dtype=dtype, device=DEV)
