@@ -53,7 +53,14 @@ TINY_C = {"architecture": "Silutar", "vocab": 130, "width": 96, "max_positions":
           "layers": [_layer(_gla(2, 72, 40, 16.0, 8), 128),
                      _layer(_cd(2, 1, 136, 32, 5, 8, 8), None),
                      _layer(_par(4, 1, 32, 16, 5, 5, 0.2, 1, 136, 8, 0.5, 2.0), 128)]}
-TINY = {"A": (TINY_A, 11, 16), "B": (TINY_B, 12, 16), "C": (TINY_C, 13, 8)}      # config, weight seed, page size
+# D: nothing is a multiple of 8 - width, feed-forward, vocabulary, head sizes, inner widths: the products and the
+#    attention that want aligned operands must find their plain forms by themselves
+TINY_D = {"architecture": "Silutar", "vocab": 77, "width": 52, "max_positions": 200, "norm": {"eps": 1e-5},
+          "logit_softcap": 25.0,
+          "layers": [_layer(_par(3, 3, 12, 12, 3, 7, 0.25, 2, 6, 5, 0.9, 0.4), 36),
+                     _layer(_gla(2, 6, 10, 4.0, 5), 50),
+                     _layer(_cd(2, 2, 10, 6, 3, 3, 7), 36)]}
+TINY = {"A": (TINY_A, 11, 16), "B": (TINY_B, 12, 16), "C": (TINY_C, 13, 8), "D": (TINY_D, 14, 4)}      # config, weight seed, page size
 
 
 def make_weights(cfg: dict, seed: int) -> Dict[str, torch.Tensor]:
@@ -117,5 +124,6 @@ def make_model_dir(path: str, which: str, store_dtype=torch.float32, cfg=None, s
 def sequences(which: str, lengths=None, seed=7) -> Dict[str, List[int]]:
     cfg = TINY[which][0]
     rnd = random.Random(seed)
-    lengths = lengths or {"A": [5, 17, 33, 70, 40, 26, 51], "B": [1, 9, 24, 50, 90, 37, 64, 12], "C": [3, 44, 21, 60, 30]}[which]
+    lengths = lengths or {"A": [5, 17, 33, 70, 40, 26, 51], "B": [1, 9, 24, 50, 90, 37, 64, 12], "C": [3, 44, 21, 60, 30],
+                          "D": [2, 31, 18, 45, 9]}[which]
     return {f"r{i}": [rnd.randrange(cfg["vocab"]) for _ in range(n)] for i, n in enumerate(lengths)}
