@@ -88,10 +88,14 @@ struct TcExtra {
     // that reads the sum next (null: no): prep_rows [T, N] bfloat16 gets (C + product) * prep_w per feature - the norm
     // without its division - and prep_sumsq [T, N / 128] the sum of squares of the new C over each tile's 128
     // features, from which the product that reads the rows forms their factor (row_sumsq there).
+    // With prep_alpha given the norm is Dynamic Tanh instead: prep_rows gets tanh(alpha * (C + product)) * prep_w +
+    // prep_b, complete rows, and no sum of squares is formed (prep_sumsq null); prep_b and prep_alpha have prep_w's type.
     const void* prep_w;
     int prep_w_f32;
     bf16* prep_rows;
     float* prep_sumsq;
+    const void* prep_b;
+    const void* prep_alpha;
     // The product is the attention's q/k/v projection with heads of 128 (a tile of 128 features is one head), reduced
     // inside a cluster: the CTAs do the per-head work on their sums themselves (h_q_out null: no) - the RMS norm of
     // query and key heads with h_q_w / h_k_w (null: none), the half-split rotation by positions[t] * inv_freq, queries
@@ -399,6 +403,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                             const uint2 wb = *reinterpret_cast<const uint2*>((const bf16*)ex.prep_w + feat);
                             const float2 w01 = __bfloat1622float2(*(const __nv_bfloat162*)&wb.x), w23 = __bfloat1622float2(*(const __nv_bfloat162*)&wb.y);
                             w = make_float4(w01.x, w01.y, w23.x, w23.y);
+                        }
+                        if (ex.prep_alpha) {
+                            // Dynamic Tanh: nothing crosses a row, the rows leave complete
+                            float4 b;
+                            float al;
+                            if (ex.prep_w_f32) { b = *reinterpret_cast<const float4*>((const float*)ex.prep_b + feat); al = *(const float*)ex.prep_alpha; }
+                            else {
+                                const uint2 bb = *reinterpret_cast<const uint2*>((const bf16*)ex.prep_b + feat);
+                                const float2 b01 = __bfloat1622float2(*(const __nv_bfloat162*)&bb.x), b23 = __bfloat1622float2(*(const __nv_bfloat162*)&bb.y);
+                                b = make_float4(b01.x, b01.y, b23.x, b23.y);
+                                al = __bfloat162float(*(const bf16*)ex.prep_alpha);
+                            }
+                            const __nv_bfloat162 a01 = __floats2bfloat162_rn(fmaf(tanhf(al * na.x), w.x, b.x), fmaf(tanhf(al * na.y), w.y, b.y));
+                            const __nv_bfloat162 a23 = __floats2bfloat162_rn(fmaf(tanhf(al * na.z), w.z, b.z), fmaf(tanhf(al * na.w), w.w, b.w));
+                            *reinterpret_cast<uint2*>(ex.prep_rows + (size_t)(t0 + cb0) * N + feat) = make_uint2(*(const uint32_t*)&a01, *(const uint32_t*)&a23);
+                            if (two) {
+                                const __nv_bfloat162 b01 = __floats2bfloat162_rn(fmaf(tanhf(al * nb.x), w.x, b.x), fmaf(tanhf(al * nb.y), w.y, b.y));
+                                const __nv_bfloat162 b23 = __floats2bfloat162_rn(fmaf(tanhf(al * nb.z), w.z, b.z), fmaf(tanhf(al * nb.w), w.w, b.w));
+                                *reinterpret_cast<uint2*>(ex.prep_rows + (size_t)(t0 + cb1) * N + feat) = make_uint2(*(const uint32_t*)&b01, *(const uint32_t*)&b23);
+                            }
+                            continue;
                         }
                         float sa = na.x * na.x + na.y * na.y + na.z * na.z + na.w * na.w;
                         float sb = nb.x * nb.x + nb.y * nb.y + nb.z * nb.z + nb.w * nb.w;
@@ -1364,7 +1389,7 @@ static int tc_extra(TcExtra* ex, const void* next_w, long long next_bytes, const
     ex->next_w = next_w; ex->next_bytes = next_w ? next_bytes : 0;
     ex->row_sumsq = row_sumsq; ex->sumsq_parts = sumsq_parts;
     ex->inv_width = row_sumsq ? 1.0f / (float)norm_width : 0.0f; ex->eps = norm_eps;
-    ex->prep_w = nullptr; ex->prep_w_f32 = 0; ex->prep_rows = nullptr; ex->prep_sumsq = nullptr;
+    ex->prep_w = nullptr; ex->prep_w_f32 = 0; ex->prep_rows = nullptr; ex->prep_sumsq = nullptr; ex->prep_b = nullptr; ex->prep_alpha = nullptr;
     ex->h_q_out = nullptr; ex->h_cache = nullptr; ex->h_kv_slot = nullptr; ex->h_positions = nullptr; ex->h_inv_freq = nullptr;
     ex->h_q_w = ex->h_k_w = nullptr; ex->h_w_f32 = 0; ex->h_QH = ex->h_KH = 0; ex->h_page = 1; ex->h_eps = 0.0f;
     return 0;
@@ -1454,7 +1479,7 @@ extern "C" int rb_gemm_bf16(const void* X, const void* W, void* C, int c_dtype, 
 extern "C" int rb_gemm_bf16_residual_norm(const void* X, const void* W, float* C, int T, int N, int K, long long ldx, long long ldw,
                                           long long ldc, const void* norm_w, int norm_w_dtype, void* prep_rows, float* prep_sumsq,
                                           const void* next_w, long long next_bytes, const float* row_sumsq, int sumsq_parts,
-                                          int norm_width, float norm_eps, void* stream) {
+                                          int norm_width, float norm_eps, const void* dyt_b, const void* dyt_alpha, void* stream) {
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0) RB_REFUSE("gemm: K=%d", K);
     if (T > 256) RB_REFUSE("gemm_residual_norm: one token tile (%d tokens)", T);
@@ -1464,11 +1489,15 @@ extern "C" int rb_gemm_bf16_residual_norm(const void* X, const void* W, float* C
         RB_REFUSE("gemm_residual_norm: 16-byte aligned sum and weight, rows 8-byte aligned (ldc %lld)", ldc);
     if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15))
         RB_REFUSE("gemm: TMA needs 16-byte aligned operands and row strides (ldx %lld, ldw %lld)", ldx, ldw);
-    if (!norm_w || !prep_rows || !prep_sumsq) RB_REFUSE("gemm: the norm's weight and both of its outputs are needed");
+    // dyt_b, dyt_alpha (the weight's dtype; both or neither): the norm is Dynamic Tanh, tanh(alpha x) w + b, its rows
+    // leave complete and prep_sumsq is not used
+    if ((dyt_b == nullptr) != (dyt_alpha == nullptr) || ((uintptr_t)dyt_b & 15)) RB_REFUSE("gemm: Dynamic Tanh needs its bias (16-byte aligned) and its alpha");
+    if (!norm_w || !prep_rows || (!prep_sumsq && !dyt_alpha)) RB_REFUSE("gemm: the norm's weight and its outputs are needed");
     if (norm_w_dtype != RB_F32 && norm_w_dtype != RB_BF16) RB_REFUSE("gemm: norm weight of dtype %d", norm_w_dtype);
     TcExtra ex;
     if (tc_extra(&ex, next_w, next_bytes, row_sumsq, sumsq_parts, norm_width, norm_eps, T)) return -1;
     ex.prep_w = norm_w; ex.prep_w_f32 = norm_w_dtype == RB_F32; ex.prep_rows = (bf16*)prep_rows; ex.prep_sumsq = prep_sumsq;
+    ex.prep_b = dyt_b; ex.prep_alpha = dyt_alpha;
     cudaStream_t s = (cudaStream_t)stream;
     const int bn = tc_bn(T);
     CUtensorMap mw, mx;

@@ -816,11 +816,14 @@ def gemm_bf16_partials(a: torch.Tensor, w: torch.Tensor, row_scale=None) -> Opti
 PRODUCT_NORM = os.environ.get("REINFER_B200_PRODUCT_NORM", "1") != "0"
 
 
-def gemm_bf16_residual_norm(a: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, norm_w: torch.Tensor, row_scale=None):
+def gemm_bf16_residual_norm(a: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, norm_w: torch.Tensor, row_scale=None,
+                            dyt=None):
     """residual[T,N] (float32) += a[T,K] @ w[N,K]^T for a decode step's few rows, the product reduced inside a
     cluster whose CTAs also prepare what the RMS norm with weight norm_w would make of the new residual: returns
     (rows, sumsq) as residual_rowscale does (rows = bfloat16(residual * norm_w), sumsq [T, N/128] the sum of squares
-    by tiles of 128 columns), or None (and does nothing) where this form does not apply."""
+    by tiles of 128 columns), or None (and does nothing) where this form does not apply.  With dyt = (bias, alpha),
+    tensors of norm_w's dtype, the norm is Dynamic Tanh: rows = bfloat16(tanh(alpha residual) norm_w + bias), complete,
+    and sumsq is None."""
     T, K = a.shape
     N = w.shape[0]
     _need(w.shape[1] == K and tuple(residual.shape) == (T, N), "gemm: shapes")
@@ -831,13 +834,20 @@ def gemm_bf16_residual_norm(a: torch.Tensor, w: torch.Tensor, residual: torch.Te
     if a.stride(1) != 1 or w.stride(1) != 1 or a.stride(0) % 8 or w.stride(0) % 8 or a.data_ptr() % 16 or w.data_ptr() % 16 or \
             residual.stride(1) != 1 or residual.stride(0) % 4 or residual.data_ptr() % 16:
         return None
+    bias = alpha = None
+    if dyt is not None:
+        bias, alpha = dyt
+        if not (bias.dtype == alpha.dtype == norm_w.dtype and bias.is_contiguous() and bias.numel() == N and alpha.numel() == 1 and
+                bias.data_ptr() % 16 == 0):
+            return None
     rows = torch.empty((T, N), dtype=torch.bfloat16, device=a.device)
-    sumsq = torch.empty((T, N // 128), dtype=torch.float32, device=a.device)
+    sumsq = torch.empty((T, N // 128), dtype=torch.float32, device=a.device) if dyt is None else None
     nw, nb = _next_range(w)
     _check(lib().rb_gemm_bf16_residual_norm(_p(a), _p(w), _p(residual), c_int(T), c_int(N), c_int(K), c_longlong(a.stride(0)),
                                             c_longlong(w.stride(0)), c_longlong(residual.stride(0)), _p(norm_w), c_int(dt(norm_w)),
-                                            _p(rows), _p(sumsq), nw, nb, *_row_scale_args(row_scale, T), _stream()),
-           f"gemm+norm {N}x{K}", 2.0 * T * N * K, 2.0 * (T * K + N * K) + 14.0 * T * N)
+                                            _p(rows), _p(sumsq), nw, nb, *_row_scale_args(row_scale, T), _p(bias), _p(alpha),
+                                            _stream()),
+           f"gemm+{'dyt' if dyt is not None else 'norm'} {N}x{K}", 2.0 * T * N * K, 2.0 * (T * K + N * K) + 14.0 * T * N)
     return rows, sumsq
 
 

@@ -50,7 +50,11 @@ class PreNormBlock:
 def _prepares(norm, reader) -> bool:
     """Whether a product before `norm` may make the norm's rows itself: the norm knows how and hands rows without
     their factor to a reader that takes them."""
-    return hasattr(norm, "prepared_by") and getattr(norm, "leaves_row_scale", False) and getattr(reader, "takes_row_scaled", False)
+    if not hasattr(norm, "prepared_by"):
+        return False
+    if getattr(norm, "prepares_complete_rows", False):        # rows that lack nothing: every reader takes them
+        return True
+    return getattr(norm, "leaves_row_scale", False) and getattr(reader, "takes_row_scaled", False)
 
 
 def _norm(norm, reader, ctx, x, delta):

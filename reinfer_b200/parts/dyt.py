@@ -12,11 +12,12 @@ import torch
 
 from .. import ops
 from ..weights.params import ParamSpec
-from .base import Norm, register_part
+from .base import Norm, PreparedRows, register_part
 
 
 class DynamicTanh(Norm):
     adds_partial_sums = True            # delta may be a stack [S, rows, width] of float32 partial sums
+    prepares_complete_rows = True       # prepared_by() leaves finished rows: any reader takes them
 
     def __init__(self, width: int, weight_name: str = "weight", bias_name: str = "bias", alpha_name: str = "alpha"):
         self.width = int(width)
@@ -35,7 +36,20 @@ class DynamicTanh(Norm):
             w, b, a = w.float(), b.float(), a.float()
         self.weight, self.bias, self.alpha = w.contiguous(), b.contiguous(), a.reshape(1).contiguous()
 
+    def prepared_by(self, ctx, a, w, residual):
+        """residual += a w^T by a product whose cluster also makes this norm's rows of the new residual (a decode step's
+        few rows, bfloat16, widths in tiles of 128): PreparedRows for forward(delta=that), or None where that form does
+        not apply and nothing was done."""
+        if self.weight is None or ctx.dtype != torch.bfloat16 or not ops.DEFER_SUMS or residual.shape[1] != self.width:
+            return None
+        made = ops.gemm_bf16_residual_norm(a, w, residual, self.weight, dyt=(self.bias, self.alpha))
+        return None if made is None else PreparedRows(self, made[0], None)
+
     def forward(self, ctx, x, out=None, delta=None, row_idx=None):
+        if isinstance(delta, PreparedRows):
+            if delta.norm is not self or out is not None or row_idx is not None:
+                raise ValueError("dyt: rows prepared by a product are for the norm they were made for")
+            return delta.rows
         if delta is not None and delta.dtype != torch.float32:
             ops.residual_add(x, delta)
             delta = None

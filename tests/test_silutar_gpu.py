@@ -169,6 +169,42 @@ def test_long_decoding_through_captured_steps(models, dtype):
     compare(got, truth(model_dir, seqs), TOL[dtype])
 
 
+def test_decode_products_do_the_next_norm_and_agree_with_the_separate_kernels(tmp_path, monkeypatch):
+    """At a width in tiles of 128 the output and down projections of a decode step add into the residual stream and
+    make the next Dynamic Tanh norm's rows in their cluster's reduction: fewer launches a step (asserted, so that a
+    silent fall back shows), the same logits to rounding as with the norm as a kernel of its own, and both follow the
+    plain implementation.  The chunk attention of this configuration (heads of 64) runs on the tensor cores."""
+    from reinfer_b200 import ops
+    from reinfer_b200.engine import Engine, StepEntry
+    d = st.make_model_dir(str(tmp_path / "e"), "E", torch.bfloat16, cfg=st.TINY_E, seed=15)
+    cfg, w = plain.read_model(d)
+    seqs = st.sequences("A", lengths=[70, 41, 9], seed=4)
+    want = {r: plain.forward(cfg, w, t) for r, t in seqs.items()}
+
+    def run(product_norm):
+        monkeypatch.setattr(ops, "PRODUCT_NORM", product_norm)
+        e = Engine.from_model_dir(d, dtype="bfloat16", page_size=16, max_tokens=512, max_num_seqs=4)
+        got = {}
+        lg = e.step([StepEntry(r, t[:-6], [len(t) - 7]) for r, t in seqs.items()])
+        for k, r in enumerate(seqs):
+            got[(r, len(seqs[r]) - 7)] = lg[k].double().cpu()
+        for i in range(6, 0, -1):
+            lg = e.step([StepEntry(r, [t[-i]], [0]) for r, t in seqs.items()])
+            for k, r in enumerate(seqs):
+                got[(r, len(seqs[r]) - i)] = lg[k].double().cpu()
+        e.check_status()
+        launches = next(iter(e._graphs.values())).n_launches
+        return got, launches
+
+    fused, n_fused = run(True)
+    apart, n_apart = run(False)
+    assert n_fused <= n_apart - 4, (n_fused, n_apart)          # at least the feed-forward norms and two mixer norms went
+    compare(fused, want, TOL["bfloat16"])
+    compare(apart, want, TOL["bfloat16"])
+    for key, row in fused.items():
+        assert (row - apart[key]).abs().max().item() <= 2e-2 * want[key[0]][key[1]].abs().max().item(), key
+
+
 def test_first_tokens_of_a_sequence(models):
     from reinfer_b200.engine import Engine, StepEntry
     for which in st.TINY:
