@@ -70,6 +70,13 @@ struct FcArgs {
     int QH, KH, page_size, page_shift, max_pages, window;
     int Gc, chunks, first_entry, n_entries;
     float scale_log2;
+    // Options for attention that is local to chunks of positions: a row sees only the keys from the start of its own
+    // chunk of `chunk` positions (a multiple of the 64-key tile; 0: off), its scores lose r1[h] ln(1 + r2[h] (i - j))
+    // (null: no penalty), and the output is multiplied by out_scale.
+    int chunk;
+    const float* r1;
+    const float* r2;
+    float out_scale;
 };
 
 struct FcShared {
@@ -243,7 +250,8 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
         tok_base = a.cu_q[e] + q0;
         bt = a.block_table + (size_t)e * a.max_pages;
         const int pos_min = start_pos + q0, pos_max = start_pos + q0 + n_tok - 1;
-        const int lo_min = a.window > 0 ? max(0, pos_min - a.window + 1) : 0;
+        int lo_min = a.window > 0 ? max(0, pos_min - a.window + 1) : 0;
+        if (a.chunk > 0) lo_min = max(lo_min, pos_min / a.chunk * a.chunk);
         t_begin = lo_min / FC_BN;
         n_tiles = pos_max / FC_BN + 1 - t_begin;
         // Q rows (row r of the CTA = token r / Gc, grouped head r % Gc; rows 128.. are tile B) into the swizzled K-major layout
@@ -377,7 +385,11 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
         const int ti = t * tpt + row / a.Gc;                       // token of the CTA
         const bool live = !none && ti < n_tok;
         const int pos = live ? start_pos + q0 + ti : -1;
-        const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+        int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+        if (a.chunk > 0) lo = max(lo, max(pos, 0) / a.chunk * a.chunk);
+        // the distance penalty of this row's head, in units of the raw score (the scale is applied to the difference)
+        const bool pen = a.r1 != nullptr;
+        const float pen_a = pen ? a.r1[head0 + row % a.Gc] / a.scale_log2 : 0.0f, pen_b = pen ? a.r2[head0 + row % a.Gc] : 0.0f;
         // m: the maximum that P and O are scaled to (it follows the true maximum only in steps larger than
         // FC_RESCALE, so that O can stay in tensor memory and be accumulated by the MMA itself); l: the sum in that scale
         float m = -INFINITY, l = 0.0f;
@@ -418,6 +430,12 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sh->s_free[t][b]));          // this buffer may take the scores of tile it + 2
+            if (pen) {                                             // (places beyond the row's position are replaced below)
+                const float dist0 = (float)(pos - k0);
+#pragma unroll
+                for (int j = 0; j < FC_BN; ++j)
+                    sr[j] = __float_as_uint(fmaf(-pen_a, __log2f(fmaf(pen_b, dist0 - (float)j, 1.0f)), __uint_as_float(sr[j])));
+            }
             if (edge) {
 #pragma unroll
                 for (int j = 0; j < FC_BN; ++j) {
@@ -516,7 +534,7 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
         if (ok && n_tiles > 0 && !*abort_flag) {
             // (the loads from tensor memory are the whole warp's: every lane takes part, only live rows store)
             tc_fence_after();
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            const float inv = l > 0.0f ? a.out_scale / l : 0.0f;
             bf16* dst = a.out + ((size_t)(tok_base + (live ? ti : 0)) * a.QH + head0 + row % a.Gc) * FC_D;
 #pragma unroll
             for (int c = 0; c < FC_D / 32; ++c) {
@@ -562,10 +580,13 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
 // entries of ceil(tokens / (256 / Gc)), Gc = the largest of 16, 8, 4, 2, 1 that divides QH / KH.
 extern "C" int rb_fa_prefill_tc(const void* q, const void* cache, long long num_pages, const int* block_table, const int* cu_q,
                                 const int* kv_len, void* out, int first_entry, int n_entries, int n_tiles, int QH, int KH, int d,
-                                int page_size, int max_pages, int window, float scale, void* stream) {
+                                int page_size, int max_pages, int window, float scale, int chunk, const float* r1, const float* r2,
+                                float out_scale, void* stream) {
     if (n_entries <= 0 || n_tiles <= 0) return 0;
     if (QH <= 0 || KH <= 0 || QH % KH) RB_REFUSE("attention: %d query heads over %d kv heads", QH, KH);
     if (d != FC_D) RB_REFUSE("attention (tcgen05): head_dim %d, only 128 is built", d);
+    // a chunk that starts inside a key tile would leave the tile's first keys to pages that may have gone back to the pool
+    if (chunk < 0 || chunk % FC_BN || (r1 == nullptr) != (r2 == nullptr)) RB_REFUSE("attention (tcgen05): chunk %d (a multiple of %d), or half a distance penalty", chunk, FC_BN);
     int shift = -1;
     for (int s = 3; s < 16; ++s) if ((1 << s) == page_size) shift = s;
     if (shift < 0) RB_REFUSE("attention (tcgen05): page size %d is not a power of two >= 8", page_size);
@@ -578,6 +599,7 @@ extern "C" int rb_fa_prefill_tc(const void* q, const void* cache, long long num_
     for (int c = 16; c >= 1; c >>= 1) if (G % c == 0) { a.Gc = c; break; }
     a.chunks = G / a.Gc; a.first_entry = first_entry; a.n_entries = n_entries;
     a.scale_log2 = scale * 1.4426950408889634f;
+    a.chunk = chunk; a.r1 = r1; a.r2 = r2; a.out_scale = out_scale;
     CUtensorMap map;
     if (rb_tensor_map_kv_pages(cache, num_pages, KH, page_size, &map)) return -1;
     constexpr size_t smem = (size_t)FC_NST * FC_STAGE + FC_TILES * 4 * FC_QHALF + sizeof(FcShared) + 1024;

@@ -473,15 +473,18 @@ def fa_prefill_tma(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n
 
 
 def fa_prefill_tc(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, q_lens,
-                  QH: int, KH: int, d: int, page_size: int, window: int, scale: float, work=(0.0, 0.0)) -> None:
+                  QH: int, KH: int, d: int, page_size: int, window: int, scale: float, work=(0.0, 0.0),
+                  chunk: int = 0, penalty=None, out_scale: float = 1.0) -> None:
     """Paged causal flash attention on the tcgen05 tensor cores (scores and the weighted sum in tensor memory):
-    head size 128, page size a power of two >= 8.  q_lens: the token counts of the entries (host)."""
+    head size 128, page size a power of two >= 8.  q_lens: the token counts of the entries (host).  chunk (a multiple
+    of 64), penalty = (r1, r2) and out_scale as in paged_attention_ref."""
     gc = int(lib().rb_fa_prefill_tc_group(c_int(QH), c_int(KH)))
     tpt = int(lib().rb_fa_prefill_tc_rows()) // gc              # tokens that one CTA takes
     n_tiles = sum(-(-int(n) // tpt) for n in q_lens)
     _check(lib().rb_fa_prefill_tc(_p(q), _p(cache), c_longlong(cache.shape[0]), _p(block_table), _p(cu_q), _p(kv_len), _p(out),
                                   c_int(first_entry), c_int(n_entries), c_int(n_tiles), c_int(QH), c_int(KH), c_int(d),
-                                  c_int(page_size), c_int(block_table.shape[1]), c_int(window), c_float(scale), _stream()),
+                                  c_int(page_size), c_int(block_table.shape[1]), c_int(window), c_float(scale), c_int(chunk),
+                                  *_penalty_args(penalty, QH), c_float(out_scale), _stream()),
            "fa_prefill_tc", *work)
 
 
@@ -973,7 +976,12 @@ def chunk_attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch
         n_splits = max(1, min(DECODE_SLOTS // max(ctas, 1), -(-chunk // 256), 16))
         fa_decode(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, 0, n_dec, 0, n_splits, QH, KH, dk, group.page_size, 0,
                   scale, work=dec_work, chunk=chunk, penalty=penalty, out_scale=out_scale)
-    if E > n_dec:
+    if E > n_dec and dk == 128 and chunk % 64 == 0 and USE_TC_ATTENTION and USE_TMA_ATTENTION and tma_pages(group.page_size):
+        # heads of 128, chunks in whole key tiles: the tcgen05 kernel
+        fa_prefill_tc(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, n_dec, E - n_dec,
+                      [ctx.q_start[e + 1] - ctx.q_start[e] for e in range(n_dec, E)], QH, KH, dk, group.page_size, 0, scale,
+                      work=pre_work, chunk=chunk, penalty=penalty, out_scale=out_scale)
+    elif E > n_dec:
         tpt = 64 // gc
         n_tiles = sum(-(-(ctx.q_start[e + 1] - ctx.q_start[e]) // tpt) for e in range(n_dec, E))
         fa_prefill(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, n_dec, E - n_dec, n_tiles, QH, KH, dk, group.page_size,

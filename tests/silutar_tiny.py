@@ -60,11 +60,12 @@ TINY_D = {"architecture": "Silutar", "vocab": 77, "width": 52, "max_positions": 
           "layers": [_layer(_par(3, 3, 12, 12, 3, 7, 0.25, 2, 6, 5, 0.9, 0.4), 36),
                      _layer(_gla(2, 6, 10, 4.0, 5), 50),
                      _layer(_cd(2, 2, 10, 6, 3, 3, 7), 36)]}
-# E: a width in tiles of 128 and heads of 64: the sizes at which a decode step's products do the next norm's work
-#    and the chunk attention runs on the tensor cores (not in TINY: its tests name it)
+# E: a width in tiles of 128, attention heads of 128 and a chunk of one key tile: the sizes at which a decode step's
+#    products do the next norm's work and the chunk attention runs on the tensor cores - prompt portions on the
+#    tcgen05 kernel, single tokens on the flash-decoding kernel (not in TINY: its tests name it)
 TINY_E = {"architecture": "Silutar", "vocab": 300, "width": 128, "max_positions": 256, "norm": {"eps": 1e-6},
           "logit_softcap": 30.0,
-          "layers": [_layer(_par(2, 1, 64, 64, 3, 32, 0.125, 2, 32, 8, 0.6, 0.9), 256),
+          "layers": [_layer(_par(2, 1, 128, 128, 3, 64, 0.09, 2, 32, 8, 0.6, 0.9), 256),
                      _layer(_cd(2, 1, 32, 64, 4, 8, 8), 256),
                      _layer(_gla(2, 32, 64, 8.0, 8), 256)]}
 TINY = {"A": (TINY_A, 11, 16), "B": (TINY_B, 12, 16), "C": (TINY_C, 13, 8), "D": (TINY_D, 14, 4)}      # config, weight seed, page size

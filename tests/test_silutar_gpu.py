@@ -173,7 +173,8 @@ def test_decode_products_do_the_next_norm_and_agree_with_the_separate_kernels(tm
     """At a width in tiles of 128 the output and down projections of a decode step add into the residual stream and
     make the next Dynamic Tanh norm's rows in their cluster's reduction: fewer launches a step (asserted, so that a
     silent fall back shows), the same logits to rounding as with the norm as a kernel of its own, and both follow the
-    plain implementation.  The chunk attention of this configuration (heads of 64) runs on the tensor cores."""
+    plain implementation.  The chunk attention of this configuration (heads of 128, a chunk of 64) runs on the tensor
+    cores: the prompts' portions on the tcgen05 kernel, the single tokens on the flash-decoding kernel."""
     from reinfer_b200 import ops
     from reinfer_b200.engine import Engine, StepEntry
     d = st.make_model_dir(str(tmp_path / "e"), "E", torch.bfloat16, cfg=st.TINY_E, seed=15)

@@ -256,7 +256,8 @@ def _paged(k, v, page, KH, dk, dv, pages_total, table):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("QH,KH,dk,dv,chunk,page", [(4, 2, 16, 24, 24, 8), (2, 2, 64, 64, 64, 16), (3, 1, 40, 8, 5, 8)])
+@pytest.mark.parametrize("QH,KH,dk,dv,chunk,page", [(4, 2, 16, 24, 24, 8), (2, 2, 64, 64, 64, 16), (3, 1, 40, 8, 5, 8),
+                                                    (4, 2, 128, 128, 64, 16), (2, 1, 128, 128, 128, 8)])
 def test_chunk_attention_sees_its_chunk_and_nothing_else(dtype, QH, KH, dk, dv, chunk, page):
     """Keys at the first position of every chunk and at the last position before it are made to stand out (a large key
     along a direction every query has a share of): the one inside must win, the one outside must not be seen, in a
