@@ -194,6 +194,7 @@ recurrence_kernel(const RecurArgs A) {
         }
         rr_cp_async_commit();
     };
+    float* opart = sm + (AHEAD ? 2 : 1) * stride;      // [TT][COLS][SPLIT] parts of the read-out
     if (AHEAD && n > 0) fetch(0, 0);
     for (int base = 0, it = 0; base < n; base += TT, ++it) {
         const int nt = min(TT, n - base);
@@ -269,10 +270,19 @@ recurrence_kernel(const RecurArgs A) {
                     s[4 * j + 3] = fmaf(kk.w, dl, s[4 * j + 3]); o4.w = fmaf(s[4 * j + 3], qq.w, o4.w);
                 }
             }
-            const float o = split_sum<SPLIT>(sum4(o4));
-            if (r == 0 && c < dv) A.out[((size_t)(s0 + base + tt) * A.H + h) * dv + c] = o;
+            // the read-out is not part of the chain from token to token: the lanes leave their parts, and the
+            // tile's sums are formed afterwards, all at once
+            opart[(tt * COLS + cl) * SPLIT + r] = sum4(o4);
         }
-        if (AHEAD) __syncthreads();                    // this buffer is refilled by the fetch after next
+        __syncthreads();                               // the parts are written; and (AHEAD) this buffer is refilled by the fetch after next
+        for (int idx = threadIdx.x; idx < nt * COLS; idx += RR_THREADS) {
+            const float* part = opart + idx * SPLIT;
+            float o = part[0];
+#pragma unroll
+            for (int i = 1; i < SPLIT; ++i) o += part[i];
+            const int tt = idx / COLS, cc = c0 + idx % COLS;
+            if (cc < dv) A.out[((size_t)(s0 + base + tt) * A.H + h) * dv + cc] = o;
+        }
     }
 #pragma unroll
     for (int ii = 0; ii < RP; ++ii) {
@@ -301,7 +311,7 @@ static int recurrence_launch(const RecurArgs& A, int n_entries, cudaStream_t st)
     constexpr int COLS = SPLIT > 4 ? 16 : RR_COLS;
     RecurArgs a = A;
     a.tile = (R::FLOATS + COLS) * 16 * sizeof(float) * (AHEAD ? 2 : 1) > 160 * 1024 || RP >= 64 ? 8 : 16;
-    const size_t smem = (size_t)a.tile * (R::FLOATS + COLS) * sizeof(float) * (AHEAD ? 2 : 1);
+    const size_t smem = (size_t)a.tile * ((R::FLOATS + COLS) * (AHEAD ? 2 : 1) + COLS * SPLIT) * sizeof(float);
     dim3 grid(rb_ceil_div(a.dv, COLS), a.H, n_entries);
     static bool done = false;                          // two buffers may pass the default limit of dynamic shared memory
     if (!done && smem > 48 * 1024) {
