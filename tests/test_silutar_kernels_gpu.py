@@ -208,9 +208,11 @@ def test_recurrence_over_portions_batches_and_reused_slots(form, gate, H, Hk, dk
         assert err < 2e-5, (r, err.item())                  # the inputs are the same rounded values on both sides
 
 
-def test_a_memory_hundreds_of_tokens_old_is_read_back():
+@pytest.mark.parametrize("form,gate", FORMS)
+def test_a_memory_hundreds_of_tokens_old_is_read_back(form, gate):
     """One key channel hardly decays; token 3 writes a value there that no later token touches (their keys are zero in
-    that channel); 600 tokens later a query on that channel reads it back, among noise from everything since."""
+    that channel, so neither a write nor a removal reaches it); 600 tokens later a query on that channel reads it
+    back, among noise from everything since.  Portions and single tokens; every form of the recurrence."""
     from reinfer_b200 import ops
     g = _gen(7)
     n, dk, dv = 640, 16, 32
@@ -218,10 +220,18 @@ def test_a_memory_hundreds_of_tokens_old_is_read_back():
     k = torch.randn(n, dk, generator=g)
     v = torch.randn(n, dv, generator=g)
     z = torch.randn(n, dk, generator=g)
+    a = torch.randn(n, dk, generator=g)
+    b = torch.randn(n, 1, generator=g) + 2.0
     k[:, 5] = 0.0
-    z[:, 5] = 14.0                                              # sigmoid(14)^(1/16): a decay of 1 - 5e-8 a token
+    k[3] = 0.0
     k[3, 5] = 6.0
+    q[603] = 0.0
     q[603, 5] = 50.0
+    # the gate of channel 5 within 1e-7 of one: sigmoid(14)^(1/16), exp(-c sigmoid(-30)), exp(-e^rate softplus(-30))
+    z[:, 5] = 14.0 if gate == "sigmoid_root" else -30.0
+    param = {"sigmoid_root": 1.0 / 16.0, "exp_sigmoid": math.exp(-0.5), "exp_softplus": 0.0}[gate]
+    rate = torch.tensor([-0.5])
+    unit = form == "delta_gated_state"
     state = torch.zeros(1, 1, dk, dv, device=DEV)
     outs = []
     at = 0
@@ -229,16 +239,30 @@ def test_a_memory_hundreds_of_tokens_old_is_read_back():
         cu, sl = _tables([m], [0])
         out = torch.empty(m, 1, dv, device=DEV)
         sel = slice(at, at + m)
-        ops.recurrence("diagonal", "sigmoid_root", q[sel].to(DEV), k[sel].to(DEV), v[sel].to(DEV), z[sel].to(DEV), None,
-                       state, out, cu, sl, 1, 1, 1, dk, dv, gate_param=1.0 / 16.0, q_scale=1.0)
+        ops.recurrence(form, gate, q[sel].to(DEV), k[sel].to(DEV), v[sel].to(DEV), z[sel].to(DEV), None,
+                       state, out, cu, sl, 1, 1, 1, dk, dv, gate_param=param, q_scale=1.0, unit_qk=unit,
+                       a_pre=a[sel].to(DEV) if form == "delta_old_state" else None,
+                       b_pre=b[sel].to(DEV) if unit else None, rate=rate.to(DEV) if gate == "exp_softplus" else None,
+                       max_q_len=m)
         outs.append(out.cpu())
         at += m
     got = torch.cat(outs)[:, 0].double()
-    gate = plain.sigmoid(z.double()) ** (1.0 / 16.0)
-    ref = plain.scan_gla(q.double(), k.double(), v.double(), gate)
-    far = 50.0 * 6.0 * v[3].double()
-    assert (ref[603] - far).abs().max() < 0.2 * far.abs().max()      # the row is that memory
+    gt = _gate64(gate, z.double().view(n, 1, dk), param, rate.double())[:, 0]
+    qd, kd = q.double(), k.double()
+    if unit:
+        qd, kd = plain.l2_unit(qd), plain.l2_unit(kd)
+    if form == "diagonal":
+        ref = plain.scan_gla(qd, kd, v.double(), gt)
+    elif form == "delta_old_state":
+        ref = plain.scan_general_delta(qd, kd, v.double(), gt, plain.sigmoid(a.double()))
+    else:
+        ref = plain.scan_gated_delta(qd, kd, v.double(), gt, plain.sigmoid(b.double())[:, 0])
+    # what token 3 wrote: k v^T, for the gated delta form the unit key times beta (v - 0)
+    wrote = 6.0 * v[3].double() if not unit else plain.sigmoid(b[3].double()) * v[3].double()
+    far = (50.0 if not unit else 1.0) * wrote
+    assert (ref[603] - far).abs().max() < 0.05 * far.abs().max()       # the row is that memory
     assert (got - ref).abs().max() < 1e-4 * ref.abs().max()
+    assert (got[603] - ref[603]).abs().max() < 1e-4 * far.abs().max()
 
 
 # ------------------------------------------------------------------ chunk attention
