@@ -68,7 +68,20 @@ TINY_E = {"architecture": "Silutar", "vocab": 300, "width": 128, "max_positions"
           "layers": [_layer(_par(2, 1, 128, 128, 3, 64, 0.09, 2, 32, 8, 0.6, 0.9), 256),
                      _layer(_cd(2, 1, 32, 64, 4, 8, 8), 256),
                      _layer(_gla(2, 32, 64, 8.0, 8), 256)]}
-TINY = {"A": (TINY_A, 11, 16), "B": (TINY_B, 12, 16), "C": (TINY_C, 13, 8), "D": (TINY_D, 14, 4)}      # config, weight seed, page size
+# F: two attention layers with different needs (two cache groups, each with block tables and a chunk of its own: 16
+#    positions = one page, and 40 positions over pages of 16), every mixer twice or in another order
+TINY_F = {"architecture": "Silutar", "vocab": 150, "width": 64, "max_positions": 300, "norm": {"eps": 1e-6},
+          "logit_softcap": 20.0,
+          "layers": [_layer(_gla(2, 16, 16, 4.0, 8), 96),
+                     _layer(_par(4, 1, 16, 16, 2, 16, 0.25, 2, 16, 8, 1.2, 0.3), None),
+                     _layer(_cd(2, 2, 16, 16, 3, 8, 8), 96),
+                     _layer(_par(2, 2, 8, 24, 4, 40, 0.35, 4, 8, 8, 0.5, 0.5), 96)]}
+# G: no attention at all: the model owns no pages, only states in the request slots
+TINY_G = {"architecture": "Silutar", "vocab": 120, "width": 48, "max_positions": 300, "norm": {"eps": 1e-6},
+          "layers": [_layer(_cd(2, 1, 24, 16, 2, 8, 8), 64),
+                     _layer(_gla(3, 8, 16, 6.0, 8), 64)]}
+TINY = {"A": (TINY_A, 11, 16), "B": (TINY_B, 12, 16), "C": (TINY_C, 13, 8), "D": (TINY_D, 14, 4), "F": (TINY_F, 16, 16),
+        "G": (TINY_G, 17, 16)}      # config, weight seed, page size
 
 
 def make_weights(cfg: dict, seed: int) -> Dict[str, torch.Tensor]:
@@ -133,5 +146,5 @@ def sequences(which: str, lengths=None, seed=7) -> Dict[str, List[int]]:
     cfg = TINY[which][0]
     rnd = random.Random(seed)
     lengths = lengths or {"A": [5, 17, 33, 70, 40, 26, 51], "B": [1, 9, 24, 50, 90, 37, 64, 12], "C": [3, 44, 21, 60, 30],
-                          "D": [2, 31, 18, 45, 9]}[which]
+                          "D": [2, 31, 18, 45, 9], "F": [4, 50, 23, 81, 36], "G": [6, 40, 17, 29]}[which]
     return {f"r{i}": [rnd.randrange(cfg["vocab"]) for _ in range(n)] for i, n in enumerate(lengths)}

@@ -97,12 +97,12 @@ def test_cuts_match_plain(models, which, dtype, cut):
     page = st.TINY[which][2]
     pool = tiny.pool_tokens_needed(steps, page)                 # not a page to spare: pages are used again
     engine = Engine.from_model_dir(model_dir, dtype=dtype, page_size=page, max_tokens=pool, max_num_seqs=4)
-    owners = tiny.PageOwners(engine.cache)
+    owners = tiny.PageOwners(engine.cache) if engine.cache.groups else None       # (a model without attention owns no pages)
     got = run_steps(engine, steps, owners)
     assert len(got) == sum(len(t) for t in seqs.values())
     compare(got, truth(model_dir, seqs), TOL[dtype])
     assert engine.cache.free_pages() == engine.cache.total_pages() and engine.cache.free_slots() == 4
-    if cut == "mixed":
+    if cut == "mixed" and owners is not None:
         assert len(owners.reused) > 0
 
 
