@@ -106,6 +106,44 @@ def test_cuts_match_plain(models, which, dtype, cut):
         assert len(owners.reused) > 0
 
 
+def cut_mixed_long(seqs, seed=5, max_live=3):
+    """Like tiny.cut_mixed with long portions too (beyond a recurrence tile of 16 and a convolution segment of 64), so
+    that one step holds a long portion of one request beside a few tokens or a single one of others."""
+    import random
+    rnd = random.Random(seed)
+    waiting, live, steps = list(seqs), {}, []
+    while waiting or live:
+        while waiting and len(live) < max_live:
+            live[waiting.pop(0)] = 0
+        entries, end = [], []
+        for r in list(live):
+            t, i = seqs[r], live[r]
+            left = len(t) - i
+            n = 1 if left <= 3 else min(rnd.choice([1, 2, 19, 33, 66, 70]), left - 3)
+            entries.append((r, t[i:i + n], list(range(n))))
+            live[r] = i + n
+            if live[r] == len(t):
+                end.append(r)
+                del live[r]
+        steps.append((entries, end))
+    return steps
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["A", "C", "F"])
+def test_long_portions_beside_single_tokens(models, which, dtype):
+    from reinfer_b200.engine import Engine
+    model_dir = models[(which, "f32" if dtype == "float32" else "bf16")]
+    seqs = st.sequences(which, lengths=[150, 9, 97, 230, 41, 72], seed=9)
+    steps = cut_mixed_long(seqs)
+    assert max(len(t) for entries, _ in steps for _, t, _ in entries) >= 66
+    page = st.TINY[which][2]
+    engine = Engine.from_model_dir(model_dir, dtype=dtype, page_size=page, max_tokens=tiny.pool_tokens_needed(steps, page), max_num_seqs=3)
+    got = run_steps(engine, steps)
+    compare(got, truth(model_dir, seqs), TOL[dtype])
+    assert engine.cache.free_pages() == engine.cache.total_pages() and engine.cache.free_slots() == 3
+
+
 @pytest.mark.parametrize("which", list(st.TINY))
 def test_float32_cuts_agree_bitwise(models, which):
     """Every 32-bit kernel orders its sums by position only: all cuts give the same bits, whatever the batch, the
