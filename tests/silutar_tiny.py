@@ -80,6 +80,13 @@ TINY_F = {"architecture": "Silutar", "vocab": 150, "width": 64, "max_positions":
 TINY_G = {"architecture": "Silutar", "vocab": 120, "width": 48, "max_positions": 300, "norm": {"eps": 1e-6},
           "layers": [_layer(_cd(2, 1, 24, 16, 2, 8, 8), 64),
                      _layer(_gla(3, 8, 16, 6.0, 8), 64)]}
+# H: a width of 256 with attention heads of 128 and recurrence heads of 64: what a small real model looks like, and where
+#    every tensor-core and fused form applies at once (not in TINY: its test names it)
+TINY_H = {"architecture": "Silutar", "vocab": 500, "width": 256, "max_positions": 512, "norm": {"eps": 1e-6},
+          "logit_softcap": 30.0,
+          "layers": [_layer(_par(4, 2, 128, 128, 3, 128, 0.09, 4, 64, 16, 0.6, 0.9), 512),
+                     _layer(_cd(4, 2, 64, 128, 4, 16, 16), 512),
+                     _layer(_gla(4, 64, 64, 16.0, 16), 512)]}
 TINY = {"A": (TINY_A, 11, 16), "B": (TINY_B, 12, 16), "C": (TINY_C, 13, 8), "D": (TINY_D, 14, 4), "F": (TINY_F, 16, 16),
         "G": (TINY_G, 17, 16)}      # config, weight seed, page size
 

@@ -144,6 +144,40 @@ def test_long_portions_beside_single_tokens(models, which, dtype):
     assert engine.cache.free_pages() == engine.cache.total_pages() and engine.cache.free_slots() == 3
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_small_real_shape_on_the_tensor_core_paths(tmp_path, dtype):
+    """Width 256, attention heads of 128 over chunks of 128, recurrence heads of 64, pages of 64 tokens: in bfloat16
+    the prompt portions' attention runs on the tcgen05 kernel, the single tokens' on flash decoding, the recurrences in
+    their wide form, the decode products with the next norm inside.  Whole prompts, tails token by token, long
+    portions beside single tokens; all against the plain implementation."""
+    from reinfer_b200.engine import Engine
+    d = st.make_model_dir(str(tmp_path / "h"), "H", torch.float32 if dtype == "float32" else torch.bfloat16, cfg=st.TINY_H, seed=18)
+    seqs = st.sequences("A", lengths=[300, 140, 37, 200], seed=12)          # (ids below the smaller vocabulary of A)
+    want = truth(d, seqs)
+    for steps in (tiny.cut_whole(seqs), tiny.cut_tail_one_by_one(seqs, tail=40), cut_mixed_long(seqs)):
+        engine = Engine.from_model_dir(d, dtype=dtype, page_size=64, max_tokens=tiny.pool_tokens_needed(steps, 64), max_num_seqs=4)
+        compare(run_steps(engine, steps), want, TOL[dtype])
+        assert engine.cache.free_pages() == engine.cache.total_pages()
+    # which kernels a prompt portion and a decode step of this shape take (a silent fall back to the plain forms would show)
+    from reinfer_b200 import ops
+    from reinfer_b200.engine import StepEntry
+    engine = Engine.from_model_dir(d, dtype=dtype, page_size=64, max_tokens=512, max_num_seqs=2, cuda_graphs=False)
+    prof = ops.SegmentProfiler()
+    old = ops.set_profiler(prof)
+    try:
+        prof.begin()
+        engine.step([StepEntry("p", seqs["r1"][:100], [99])])
+        engine.step([StepEntry("p", seqs["r1"][100:101], [0])])
+    finally:
+        ops.set_profiler(old)
+    names = set(prof.summary())
+    if dtype == "bfloat16":
+        assert {"fa_prefill_tc", "fa_decode"} <= names and any(n.startswith("gemm+dyt") for n in names), names
+        assert "paged_attention_ref" not in names and not any(n.startswith("gemm_fma") for n in names), names
+    else:
+        assert "paged_attention_ref" in names and any(n.startswith("gemm_fma") for n in names), names
+
+
 @pytest.mark.parametrize("which", list(st.TINY))
 def test_float32_cuts_agree_bitwise(models, which):
     """Every 32-bit kernel orders its sums by position only: all cuts give the same bits, whatever the batch, the
