@@ -119,3 +119,5 @@ def _ensure_builtin() -> None:
     _q.register()
     from ..models import silutar as _s
     _s.register()
+    from ..models import damadra as _d
+    _d.register()

@@ -8,7 +8,8 @@
 // the faster bfloat16 kernels.
 // Beyond the plain form it takes: a value head size of its own (dv != d), a chunk mask (a token sees the
 // keys of its own chunk of `chunk` positions, counted from position 0), a logarithmic distance penalty per
-// query head (score -= r1[h] * ln(1 + r2[h] * (i - j))), and a factor on the output.
+// query head (score -= r1[h] * ln(1 + r2[h] * (i - j))), a learned bias by distance (score += bias[min(i - j,
+// rows - 1)][h], a float table [rows, QH] whose last row stands for every greater distance), and a factor on the output.
 // (reference semantics: crates/cuda/kernels/decode_gqa_kernels.cu:99-136 page lookup
 //  page[t/block_len]; decode_flash_kernels.cu:212-349 max/exp/sum/PV in f32.)
 #include "common.cuh"
@@ -28,7 +29,8 @@ paged_attention_ref_kernel(const TA* __restrict__ q, const TC* __restrict__ cach
                            const int* __restrict__ block_table, const int* __restrict__ tok_row,
                            const int* __restrict__ positions, TA* __restrict__ out,
                            int QH, int KH, int d, int dv, int page_size, int max_pages, int window, float scale,
-                           int chunk, const float* __restrict__ r1, const float* __restrict__ r2, float out_scale) {
+                           int chunk, const float* __restrict__ r1, const float* __restrict__ r2, float out_scale,
+                           const float* __restrict__ bias, int bias_rows) {
     pdl_trigger(); pdl_wait();
     extern __shared__ float qs_all[];                         // RA_WARPS * d floats
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -70,6 +72,7 @@ paged_attention_ref_kernel(const TA* __restrict__ q, const TC* __restrict__ cach
             for (int i = 0; i < d; ++i) dot = fmaf(qs[i], to_f32(krow[i]), dot);
             s = dot * scale;
             if (r1) s -= pen1 * log1pf(pen2 * (float)(pos - key));
+            if (bias) s += bias[(size_t)min(pos - key, bias_rows - 1) * QH + hq];
         }
         const float bm = warp_max(s);
         if (bm == -INFINITY) continue;                         // no key in this block (warp-uniform)
@@ -102,27 +105,29 @@ paged_attention_ref_kernel(const TA* __restrict__ q, const TC* __restrict__ cach
 }
 
 // dv: the value heads' size (0: as d).  chunk 0: no chunk mask.  r1, r2 [QH] float: the distance penalty (null: none).
+// bias [bias_rows, QH] float: the bias by distance (null: none).
 extern "C" int rb_paged_attention_ref(const void* q, const void* cache, int dtype,
                                       const int* block_table, const int* tok_row, const int* positions,
                                       void* out, int n_tokens, int QH, int KH, int d, int page_size,
                                       int max_pages, int window, float scale, int dv, int chunk, const float* r1,
-                                      const float* r2, float out_scale, void* stream) {
+                                      const float* r2, float out_scale, const float* bias, int bias_rows, void* stream) {
     if (n_tokens <= 0) return 0;
     if (dv <= 0) dv = d;
     if (QH <= 0 || KH <= 0 || QH % KH != 0) RB_REFUSE("attention: %d query heads over %d kv heads", QH, KH);
     if (d <= 0 || d > RA_MAX_D || dv > RA_MAX_D) RB_REFUSE("attention: head sizes %d, %d (supported: 1..%d)", d, dv, RA_MAX_D);
     if (page_size <= 0 || max_pages <= 0) RB_REFUSE("attention: page_size %d max_pages %d", page_size, max_pages);
     if (chunk < 0 || (r1 == nullptr) != (r2 == nullptr)) RB_REFUSE("attention: chunk %d, or half a distance penalty", chunk);
+    if (bias && bias_rows <= 0) RB_REFUSE("attention: a distance bias of %d rows", bias_rows);
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_tokens, rb_ceil_div(QH, RA_WARPS));
     const size_t smem = (size_t)RA_WARPS * d * sizeof(float);
     if (dtype == RB_F32)
         return rb_launch(paged_attention_ref_kernel<float, float>, grid, dim3(RA_WARPS * 32), smem, s,
             (const float*)q, (const float*)cache, block_table, tok_row, positions, (float*)out,
-            QH, KH, d, dv, page_size, max_pages, window, scale, chunk, r1, r2, out_scale);
+            QH, KH, d, dv, page_size, max_pages, window, scale, chunk, r1, r2, out_scale, bias, bias_rows);
     if (dtype == RB_BF16)
         return rb_launch(paged_attention_ref_kernel<bf16, bf16>, grid, dim3(RA_WARPS * 32), smem, s,
             (const bf16*)q, (const bf16*)cache, block_table, tok_row, positions, (bf16*)out,
-            QH, KH, d, dv, page_size, max_pages, window, scale, chunk, r1, r2, out_scale);
+            QH, KH, d, dv, page_size, max_pages, window, scale, chunk, r1, r2, out_scale, bias, bias_rows);
     RB_REFUSE("attention: dtype %d", dtype);
 }

@@ -7,11 +7,14 @@
 // ---------------------------------------------------------------- embedding
 // x[t,:] = E[ids[t],:]   (reference: crates/cuda/kernels/dense_kernels.cu:329-336)
 // With a table of learned position vectors, x[t,:] = E[ids[t],:] + P[positions[t],:], the sum in float.
+// `scale` multiplies the row (and the position vector's sum) in float; `rounded`, if given, receives the same
+// rows in bfloat16 (for a first layer whose products read the stream itself rather than a norm of it).
 template <typename TW>
 __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
                                     const int* __restrict__ slot_token, const int* __restrict__ entry_slot,
                                     const int* __restrict__ tok_entry, float* __restrict__ out, int h, int vocab,
-                                    const TW* __restrict__ pos_table, const int* __restrict__ positions, int max_pos) {
+                                    const TW* __restrict__ pos_table, const int* __restrict__ positions, int max_pos,
+                                    float scale, bf16* __restrict__ rounded) {
     pdl_trigger(); pdl_wait();
     const int t = blockIdx.x;
     int id = ids[t];
@@ -21,14 +24,21 @@ __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __r
     const bool ok = (id >= 0 && id < vocab);          // the host refuses other ids before launching
     const TW* row = table + (size_t)(ok ? id : 0) * h;
     float* o = out + (size_t)t * h;
+    bf16* ro = rounded ? rounded + (size_t)t * h : nullptr;
+    const TW* prow = nullptr;
+    bool pok = false;
     if (pos_table) {
         const int p = positions[t];
-        const bool pok = (p >= 0 && p < max_pos);     // the host refuses a request longer than the table
-        const TW* prow = pos_table + (size_t)(pok ? p : 0) * h;
-        for (int i = threadIdx.x; i < h; i += blockDim.x) o[i] = (ok ? to_f32(row[i]) : 0.0f) + (pok ? to_f32(prow[i]) : 0.0f);
-        return;
+        pok = (p >= 0 && p < max_pos);                // the host refuses a request longer than the table
+        prow = pos_table + (size_t)(pok ? p : 0) * h;
     }
-    for (int i = threadIdx.x; i < h; i += blockDim.x) o[i] = ok ? to_f32(row[i]) : 0.0f;
+    for (int i = threadIdx.x; i < h; i += blockDim.x) {
+        float v = ok ? to_f32(row[i]) : 0.0f;
+        if (pok) v += to_f32(prow[i]);
+        if (scale != 1.0f) v *= scale;
+        o[i] = v;
+        if (ro) ro[i] = __float2bfloat16_rn(v);
+    }
 }
 
 // slot_token [slots], entry_slot [entries], tok_entry [tokens]: all three, or none (then every id must be >= 0).
@@ -36,7 +46,7 @@ __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __r
 extern "C" int rb_embed_gather(const void* table, int table_dtype, const int* ids, const int* slot_token,
                                const int* entry_slot, const int* tok_entry, float* out,
                                int n_tokens, int h, int vocab, const void* pos_table, const int* positions, int max_pos,
-                               void* stream) {
+                               float scale, void* rounded, void* stream) {
     if (n_tokens <= 0) return 0;
     if (h <= 0 || vocab <= 0) RB_REFUSE("embed_gather: hidden=%d vocab=%d", h, vocab);
     if (slot_token && (!entry_slot || !tok_entry)) RB_REFUSE("embed_gather: tokens from slots need the slot of each entry and the entry of each token");
@@ -45,10 +55,12 @@ extern "C" int rb_embed_gather(const void* table, int table_dtype, const int* id
     const int threads = h >= 1024 ? 256 : 128;
     if (table_dtype == RB_F32)
         return rb_launch(embed_gather_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (const float*)table, ids,
-                         slot_token, entry_slot, tok_entry, out, h, vocab, (const float*)pos_table, positions, max_pos);
+                         slot_token, entry_slot, tok_entry, out, h, vocab, (const float*)pos_table, positions, max_pos,
+                         scale, (bf16*)rounded);
     if (table_dtype == RB_BF16)
         return rb_launch(embed_gather_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, (const bf16*)table, ids,
-                         slot_token, entry_slot, tok_entry, out, h, vocab, (const bf16*)pos_table, positions, max_pos);
+                         slot_token, entry_slot, tok_entry, out, h, vocab, (const bf16*)pos_table, positions, max_pos,
+                         scale, (bf16*)rounded);
     RB_REFUSE("embed_gather: table dtype %d", table_dtype);
 }
 

@@ -1,0 +1,132 @@
+// What stands between the q/k/v projection and an attention without a rotation: the RMS norm of the queries and
+// of the keys - per head with one weight [d] for all heads, or over the whole projection with a weight of that
+// size - an optional warm-up factor on the queries that grows with the logarithm of the position,
+//     q *= 1 + coef * ln(floor((p + 1) / every) + 1),
+// and the stores: queries to [T, QH, d], normalised keys and the values into the token's place in the paged cache.
+// The values are a projection of their own, or the keys as projected (before their norm).  A layer that reads
+// another layer's keys and values prepares its queries only.  One CTA per token; arithmetic in float.
+#include "common.cuh"
+
+#define HP_THREADS 128
+
+// sum of squares of `n` floats in shared memory by the whole CTA (n == width of a group that spans all heads)
+__device__ __forceinline__ float hp_block_sumsq(const float* v, int n, float* red) {
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) ss += v[i] * v[i];
+    return block_sum(ss, red);
+}
+
+// x [T, stride]: queries at column 0 (QH*d), keys behind them (KH*d), then the values (KH*dv) unless they are the keys.
+// q_group / k_group: the width one norm spans (d: per head, weight [d]; QH*d or KH*d: the whole projection, weight of
+// that size).  kv_slot null: nothing is stored and the keys are not read.
+template <typename TA, typename TW, typename TC>
+__global__ void __launch_bounds__(HP_THREADS)
+norm_heads_append_kernel(const TA* __restrict__ x, long long stride, const TW* __restrict__ qw, const TW* __restrict__ kw,
+                         const int* __restrict__ positions, const int* __restrict__ kv_slot, TA* __restrict__ q_out,
+                         TC* __restrict__ cache, int QH, int KH, int d, int dv, int q_group, int k_group, int values_are_keys,
+                         int page_size, float eps, float temp_coef, int temp_every) {
+    extern __shared__ float sm[];                              // q [QH*d] | k [KH*d]
+    __shared__ float red[32];
+    __shared__ float inv_q[64], inv_k[64];                     // per-head factors (per-head norms of up to 64 heads a pass)
+    pdl_trigger(); pdl_wait();
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int nq = QH * d, nk = KH * d;
+    const TA* xr = x + (size_t)t * stride;
+    float* sq = sm;
+    float* sk = sm + nq;
+    const int slot = kv_slot ? kv_slot[t] : -1;
+    const bool store = slot >= 0;                              // a padding row of a captured step stores nothing
+    for (int i = threadIdx.x; i < nq; i += blockDim.x) sq[i] = to_f32(xr[i]);
+    if (store) for (int i = threadIdx.x; i < nk; i += blockDim.x) sk[i] = to_f32(xr[nq + i]);
+    __syncthreads();
+    float temp = 1.0f;
+    if (temp_every > 0) temp = 1.0f + temp_coef * logf((float)((positions[t] + 1) / temp_every) + 1.0f);
+
+    // ---- queries
+    if (q_group == nq) {
+        const float f = temp / sqrtf(hp_block_sumsq(sq, nq, red) / (float)nq + eps);
+        for (int i = threadIdx.x; i < nq; i += blockDim.x)
+            q_out[(size_t)t * nq + i] = from_f32<TA>(sq[i] * f * to_f32(qw[i]));
+    } else {
+        for (int h0 = 0; h0 < QH; h0 += 64) {
+            for (int h = h0 + warp; h < min(QH, h0 + 64); h += nwarps) {
+                float ss = 0.0f;
+                for (int i = lane; i < d; i += 32) ss += sq[h * d + i] * sq[h * d + i];
+                ss = warp_sum(ss);
+                if (lane == 0) inv_q[h - h0] = temp / sqrtf(ss / (float)d + eps);
+            }
+            __syncthreads();
+            const int n = min(QH - h0, 64) * d;
+            for (int i = threadIdx.x; i < n; i += blockDim.x)
+                q_out[(size_t)t * nq + h0 * d + i] = from_f32<TA>(sq[h0 * d + i] * inv_q[i / d] * to_f32(qw[i % d]));
+            __syncthreads();
+        }
+    }
+    if (!store) return;
+
+    // ---- keys and values into the token's place: page [K: KH x page x d | V: KH x page x dv]
+    const int page = slot / page_size, off = slot % page_size;
+    const size_t page_stride = (size_t)KH * page_size * (d + dv);
+    TC* kdst = cache + (size_t)page * page_stride + (size_t)off * d;
+    TC* vdst = cache + (size_t)page * page_stride + (size_t)KH * page_size * d + (size_t)off * dv;
+    if (values_are_keys) {
+        for (int i = threadIdx.x; i < nk; i += blockDim.x)
+            vdst[(size_t)(i / d) * page_size * dv + i % d] = from_f32<TC>(sk[i]);
+    } else {
+        const TA* xv = xr + nq + nk;
+        for (int i = threadIdx.x; i < KH * dv; i += blockDim.x)
+            vdst[(size_t)(i / dv) * page_size * dv + i % dv] = from_f32<TC>(to_f32(xv[i]));
+    }
+    if (k_group == nk) {
+        const float f = 1.0f / sqrtf(hp_block_sumsq(sk, nk, red) / (float)nk + eps);
+        for (int i = threadIdx.x; i < nk; i += blockDim.x)
+            kdst[(size_t)(i / d) * page_size * d + i % d] = from_f32<TC>(sk[i] * f * to_f32(kw[i]));
+    } else {
+        for (int h0 = 0; h0 < KH; h0 += 64) {
+            for (int h = h0 + warp; h < min(KH, h0 + 64); h += nwarps) {
+                float ss = 0.0f;
+                for (int i = lane; i < d; i += 32) ss += sk[h * d + i] * sk[h * d + i];
+                ss = warp_sum(ss);
+                if (lane == 0) inv_k[h - h0] = 1.0f / sqrtf(ss / (float)d + eps);
+            }
+            __syncthreads();
+            const int n = min(KH - h0, 64) * d;
+            for (int i = threadIdx.x; i < n; i += blockDim.x) {
+                const int h = h0 + i / d;
+                kdst[(size_t)h * page_size * d + i % d] = from_f32<TC>(sk[h * d + i % d] * inv_k[i / d] * to_f32(kw[i % d]));
+            }
+            __syncthreads();
+        }
+    }
+}
+
+extern "C" int rb_norm_heads_append(const void* x, long long stride, int dtype, const void* qw, const void* kw, int w_dtype,
+                                    const int* positions, const int* kv_slot, void* q_out, void* cache,
+                                    int T, int QH, int KH, int d, int dv, int q_group, int k_group, int values_are_keys,
+                                    int page_size, float eps, float temp_coef, int temp_every, void* stream) {
+    if (T <= 0) return 0;
+    if (QH <= 0 || KH <= 0 || d <= 0 || dv <= 0) RB_REFUSE("norm_heads_append: %d query heads, %d key heads of %d, values of %d", QH, KH, d, dv);
+    if (q_group != d && q_group != QH * d) RB_REFUSE("norm_heads_append: a query norm over %d of %d x %d", q_group, QH, d);
+    if (kv_slot && k_group != d && k_group != KH * d) RB_REFUSE("norm_heads_append: a key norm over %d of %d x %d", k_group, KH, d);
+    if (values_are_keys && dv != d) RB_REFUSE("norm_heads_append: values that are the keys have the keys' size");
+    if (temp_every > 0 && !positions) RB_REFUSE("norm_heads_append: the queries' warm-up needs the positions");
+    if (kv_slot && (!cache || page_size <= 0 || !kw)) RB_REFUSE("norm_heads_append: storing needs a cache, a page size and the keys' norm");
+    if (!qw) RB_REFUSE("norm_heads_append: the queries' norm weight is missing");
+    const size_t smem = (size_t)(QH + KH) * d * sizeof(float);
+    if (smem > 200 * 1024) RB_REFUSE("norm_heads_append: %d floats of queries and keys per token", (QH + KH) * d);
+    cudaStream_t s = (cudaStream_t)stream;
+#define RB_HP(TA, TW) do { \
+        if (smem > 48 * 1024) { \
+            cudaError_t e = cudaFuncSetAttribute(norm_heads_append_kernel<TA, TW, TA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) return (int)e; \
+        } \
+        return rb_launch(norm_heads_append_kernel<TA, TW, TA>, dim3(T), dim3(HP_THREADS), smem, s, (const TA*)x, stride, \
+                         (const TW*)qw, (const TW*)kw, positions, kv_slot, (TA*)q_out, (TA*)cache, QH, KH, d, dv, q_group, k_group, \
+                         values_are_keys, page_size, eps, temp_coef, temp_every); } while (0)
+    if (dtype == RB_F32 && w_dtype == RB_F32) RB_HP(float, float);
+    if (dtype == RB_BF16 && w_dtype == RB_BF16) RB_HP(bf16, bf16);
+    if (dtype == RB_BF16 && w_dtype == RB_F32) RB_HP(bf16, float);
+#undef RB_HP
+    RB_REFUSE("norm_heads_append: dtypes %d, %d", dtype, w_dtype);
+}

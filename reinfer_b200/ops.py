@@ -171,19 +171,24 @@ def _need(cond: bool, msg: str) -> None:
 # ------------------------------------------------------------------ wrappers
 def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, slot_token: Optional[torch.Tensor] = None,
                  entry_slot: Optional[torch.Tensor] = None, tok_entry: Optional[torch.Tensor] = None,
-                 pos_table: Optional[torch.Tensor] = None, positions: Optional[torch.Tensor] = None) -> None:
+                 pos_table: Optional[torch.Tensor] = None, positions: Optional[torch.Tensor] = None,
+                 scale: float = 1.0, rounded: Optional[torch.Tensor] = None) -> None:
     """out[t,:] (float32) = table[ids[t],:]; where ids[t] < 0 and the slot tables are given, the id is
     slot_token[entry_slot[tok_entry[t]]]: the token that the sampler left in the request's slot.  With a table of
-    learned position vectors (the embedding table's dtype) the row pos_table[positions[t]] is added."""
+    learned position vectors (the embedding table's dtype) the row pos_table[positions[t]] is added.  `scale`
+    multiplies the rows; `rounded` (bfloat16, out's shape) receives them once more, rounded."""
     _need(out.dtype == torch.float32 and ids.dtype == torch.int32, "embed_gather: out float32, ids int32")
     _need(table.is_contiguous() and out.is_contiguous(), "embed_gather: contiguous tensors")
+    _need(rounded is None or (rounded.dtype == torch.bfloat16 and rounded.is_contiguous() and rounded.shape == out.shape),
+          "embed_gather: the rounded copy is bfloat16 of out's shape")
     if pos_table is not None:
         _need(pos_table.dtype == table.dtype and pos_table.is_contiguous() and pos_table.shape[1] == table.shape[1] and
               positions is not None, "embed_gather: a position table of the embedding's dtype and width, with positions")
     _check(lib().rb_embed_gather(_p(table), dt(table), _p(ids), _p(slot_token), _p(entry_slot), _p(tok_entry), _p(out),
                                  c_int(ids.numel()), c_int(table.shape[1]), c_int(table.shape[0]),
                                  _p(pos_table), _p(positions if pos_table is not None else None),
-                                 c_int(pos_table.shape[0] if pos_table is not None else 0), _stream()), "embed_gather")
+                                 c_int(pos_table.shape[0] if pos_table is not None else 0), c_float(float(scale)),
+                                 _p(rounded), _stream()), "embed_gather")
 
 
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor, out: torch.Tensor,
@@ -291,11 +296,11 @@ def gemm_ref(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, accumulate: bool
 def paged_attention_ref(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, tok_row: torch.Tensor,
                         positions: torch.Tensor, out: torch.Tensor, QH: int, KH: int, d: int, page_size: int,
                         window: int, scale: float, work=(0.0, 0.0), dv: int = 0, chunk: int = 0,
-                        penalty=None, out_scale: float = 1.0) -> None:
+                        penalty=None, out_scale: float = 1.0, bias: Optional[torch.Tensor] = None) -> None:
     """The plain attention over the paged cache.  dv: the value heads' size where it differs from d (the cache of a
     layer is then [page][K: KH x page x d | V: KH x page x dv]); chunk: a token sees only the keys of its own chunk
     of that many positions; penalty = (r1, r2), float32 [QH] each: score -= r1 ln(1 + r2 (i - j)); out_scale
-    multiplies the output before it is rounded."""
+    multiplies the output before it is rounded; bias: float32 [rows, QH], score += bias[min(i - j, rows - 1), h]."""
     _need(q.is_contiguous() and out.is_contiguous() and cache.is_contiguous() and block_table.is_contiguous(),
           "attention: contiguous")
     _need(q.dtype == cache.dtype == out.dtype, "attention: one dtype for q, cache and out")
@@ -307,8 +312,17 @@ def paged_attention_ref(q: torch.Tensor, cache: torch.Tensor, block_table: torch
     _check(lib().rb_paged_attention_ref(_p(q), _p(cache), c_int(dt(q)), _p(block_table), _p(tok_row), _p(positions),
                                         _p(out), c_int(q.shape[0]), c_int(QH), c_int(KH), c_int(d), c_int(page_size),
                                         c_int(block_table.shape[1]), c_int(window), c_float(scale), c_int(dv), c_int(chunk),
-                                        _p(r1), _p(r2), c_float(out_scale), _stream()),
+                                        _p(r1), _p(r2), c_float(out_scale), *_bias_args(bias, QH), _stream()),
            "paged_attention_ref", *work)
+
+
+def _bias_args(bias, QH: int):
+    """(pointer, rows) of a distance-bias table: float32 [rows, QH], the last row for every greater distance."""
+    if bias is None:
+        return c_void_p(0), c_int(0)
+    _need(bias.dtype == torch.float32 and bias.is_contiguous() and bias.dim() == 2 and bias.shape[1] == QH and bias.shape[0] > 0,
+          "attention: the distance bias is a float32 table [rows, query heads]")
+    return _p(bias), c_int(bias.shape[0])
 
 
 def fa_group_chunk(group: int) -> int:
@@ -986,6 +1000,95 @@ def chunk_attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch
         n_tiles = sum(-(-(ctx.q_start[e + 1] - ctx.q_start[e]) // tpt) for e in range(n_dec, E))
         fa_prefill(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, n_dec, E - n_dec, n_tiles, QH, KH, dk, group.page_size,
                    0, scale, work=pre_work, chunk=chunk, penalty=penalty, out_scale=out_scale)
+
+
+def residual_outnorm(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float, mult: float,
+                     rounded: Optional[torch.Tensor] = None) -> None:
+    """x (float32 [rows, h]) += mult * rms(y) * w with y float32 [rows, h] or a stack [S, rows, h] of partial sums
+    (added in ascending order) and rms(y) = y / sqrt(mean(y^2) + eps); `rounded` (bfloat16 [rows, h]) receives
+    the new x once more, rounded."""
+    _need(x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2, "outnorm: x float32 [rows, h] contiguous")
+    rows, h = x.shape
+    _need(y.dtype == torch.float32 and y.is_contiguous() and y.shape[-1] == h and y.numel() % max(x.numel(), 1) == 0 and y.numel() >= x.numel(),
+          "outnorm: y float32 with x's shape (or a stack of it)")
+    _need(rounded is None or (rounded.dtype == torch.bfloat16 and rounded.is_contiguous() and rounded.shape == x.shape),
+          "outnorm: the rounded copy is bfloat16 of x's shape")
+    if rows == 0:
+        return
+    _check(lib().rb_residual_outnorm(_p(x), _p(y), c_int(y.numel() // x.numel()), c_longlong(x.numel()), _p(w), c_int(dt(w)),
+                                     _p(rounded), c_int(rows), c_int(h), c_float(eps), c_float(mult), _stream()),
+           "residual_outnorm", 0.0, float((y.numel() + 2 * x.numel()) * 4 + (2 * x.numel() if rounded is not None else 0)))
+
+
+def round_rows(x: torch.Tensor) -> torch.Tensor:
+    """bfloat16 copy of float32 rows."""
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "round_rows: float32 contiguous")
+    out = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+    _check(lib().rb_round_rows(_p(x), _p(out), c_longlong(x.numel()), _stream()), "round_rows", 0.0, 6.0 * x.numel())
+    return out
+
+
+def norm_heads_append(x: torch.Tensor, qw: torch.Tensor, kw: Optional[torch.Tensor], positions: Optional[torch.Tensor],
+                      kv_slot: Optional[torch.Tensor], q_out: torch.Tensor, cache: Optional[torch.Tensor],
+                      QH: int, KH: int, d: int, dv: int, q_group: int, k_group: int, values_are_keys: bool, page_size: int,
+                      eps: float, temp=None) -> None:
+    """x [T, q | k | v] (v absent when the values are the keys): RMS norm of q over groups of q_group columns (d: per
+    head with a weight [d]; QH*d: the whole projection) and of k likewise, q times 1 + coef ln(floor((p+1)/every) + 1)
+    with temp = (coef, every), q -> q_out [T, QH, d], normalised k and the values (projected, or k before its norm)
+    into the token's cache slot.  kv_slot None: only the queries are prepared."""
+    _need(x.stride(1) == 1 and q_out.is_contiguous() and x.dtype == q_out.dtype, "norm_heads_append: rows contiguous, one dtype")
+    need = QH * d if kv_slot is None else (QH + KH) * d + (0 if values_are_keys else KH * dv)
+    _need(x.shape[1] >= need, "norm_heads_append: x holds q | k | v")
+    _need(cache is None or cache.dtype == x.dtype, "norm_heads_append: the cache has the activations' dtype")
+    _need(kw is None or kw.dtype == qw.dtype, "norm_heads_append: norm weights of one dtype")
+    coef, every = (float(temp[0]), int(temp[1])) if temp is not None else (0.0, 0)
+    _check(lib().rb_norm_heads_append(_p(x), c_longlong(x.stride(0)), c_int(dt(x)), _p(qw), _p(kw), c_int(dt(qw)),
+                                      _p(positions), _p(kv_slot), _p(q_out), _p(cache if kv_slot is not None else None),
+                                      c_int(x.shape[0]), c_int(QH), c_int(KH), c_int(d), c_int(dv), c_int(q_group), c_int(k_group),
+                                      c_int(int(bool(values_are_keys))), c_int(page_size), c_float(eps), c_float(coef), c_int(every),
+                                      _stream()), "norm_heads_append")
+
+
+def moe_route(z: torch.Tensor, corr: Optional[torch.Tensor], experts: int, top: int):
+    """z float32 [T, n] router outputs -> (gates float32 [T, experts], ident float32 [T] or None): softmax over all n,
+    the `top` largest of score + corr chosen, gates = the chosen scores (zero elsewhere), ident = the sum of the chosen
+    scores among the outputs experts..n-1 (experts that are the identity)."""
+    _need(z.dtype == torch.float32 and z.is_contiguous() and z.dim() == 2, "moe_route: z float32 [T, n]")
+    T, n = z.shape
+    _need(corr is None or (corr.dtype == torch.float32 and corr.numel() == n), "moe_route: the correction is float32 [n]")
+    gates = torch.empty((T, experts), dtype=torch.float32, device=z.device)
+    ident = torch.empty((T,), dtype=torch.float32, device=z.device) if n > experts else None
+    _check(lib().rb_moe_route(_p(z), _p(corr), _p(gates), _p(ident), c_int(T), c_int(n), c_int(experts), c_int(top), _stream()),
+           "moe_route")
+    return gates, ident
+
+
+def relu2_gate(u: torch.Tensor, gates: torch.Tensor, ff: int) -> torch.Tensor:
+    """act[t, e*ff + c] = relu(u[t, e*ff + c])^2 * gates[t, e], in u's dtype."""
+    T, E = gates.shape
+    _need(u.is_contiguous() and u.shape == (T, E * ff) and gates.dtype == torch.float32 and gates.is_contiguous(),
+          "relu2_gate: u [T, experts * ff], gates float32 [T, experts]")
+    act = torch.empty_like(u)
+    _check(lib().rb_relu2_gate(_p(u), _p(gates), _p(act), c_int(dt(u)), c_int(T), c_int(E), c_int(ff), _stream()), "relu2_gate",
+           0.0, 2.0 * u.numel() * u.element_size())
+    return act
+
+
+def rows_axpy(dst: torch.Tensor, a: torch.Tensor, src: torch.Tensor, store: bool = False) -> None:
+    """dst[t,:] (float32) += a[t] * src[t,:]  (store: = instead of +=)."""
+    _need(dst.dtype == torch.float32 and dst.is_contiguous() and src.is_contiguous() and dst.shape == src.shape and
+          a.dtype == torch.float32 and a.numel() == dst.shape[0], "rows_axpy: dst float32 [T, h], a float32 [T], src [T, h]")
+    _check(lib().rb_rows_axpy(_p(dst), _p(a), _p(src), c_int(dt(src)), c_int(dst.shape[0]), c_int(dst.shape[1]),
+                              c_int(int(store)), _stream()), "rows_axpy")
+
+
+def biased_attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch.Tensor, QH: int, KH: int, dk: int, dv: int,
+                     window: int, scale: float, bias: Optional[torch.Tensor]) -> None:
+    """Softmax attention of a step's tokens over their requests' pages, causal or in a sliding window, with a
+    learned bias by distance (float32 [rows, QH]; the last row serves every greater distance) added to the scaled
+    scores, and value heads of their own size.  q [T, QH, dk], out [T, QH, dv]."""
+    paged_attention_ref(q, cache, group.block_table, ctx.tok_entry, ctx.positions, out, QH, KH, dk, group.page_size, window, scale,
+                        dv=dv, bias=bias)
 
 
 RECURRENCE_FORMS = {"diagonal": 0, "delta_old_state": 1, "delta_gated_state": 2}

@@ -194,3 +194,4 @@ def _ensure_builtin() -> None:
     _done = True
     from . import norm, rope, attention, ffn, embedding, block  # noqa: F401  (each registers itself)
     from . import dyt, chunk_attention, linear_recurrence, parallel  # noqa: F401
+    from . import biased_attention, moe  # noqa: F401

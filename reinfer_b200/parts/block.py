@@ -9,7 +9,10 @@ the block hands it to the norm that reads x next, which adds it on the way; what
 feed-forward leaves is the block's own result, for the norm of the next block."""
 from __future__ import annotations
 
-from .base import register_part
+import torch
+
+from .. import ops
+from .base import PreparedRows, register_part
 
 
 def need_roles(block_name: str, parts, roles) -> None:
@@ -85,5 +88,69 @@ class PreNormMixerBlock:
         return self.mixer_norm if _prepares(self.mixer_norm, self.mixer) else None
 
 
+class OutNormBlock:
+    """x += m * norm1(mixer(x));  x += m * norm2(ffn(x)): the sublayers read the stream itself and the norm (kind
+    `rms_out`, which also holds m) sits on what they put out.  A sublayer gets a fresh float32 tensor in the place of
+    the residual (`ctx.fresh_residual`: its last product stores there, or leaves partial sums) and the norm's
+    kernel adds the normalised rows to x.  In bfloat16 the products read the stream's rounding, which the kernel
+    that last wrote the stream leaves beside it (`ctx.rounded_stream`).  The feed-forward is optional."""
+    roles = ("mixer", "mixer_norm")
+    hands_on_sums = True
+    reads_rounded_stream = True
+
+    def __init__(self, parts):
+        need_roles("out_norm", parts, self.roles)
+        self.mixer, self.mixer_norm = parts["mixer"], parts["mixer_norm"]
+        self.ffn, self.ffn_norm = parts.get("ffn"), parts.get("ffn_norm")
+        if (self.ffn is None) != (self.ffn_norm is None):
+            raise ValueError("block 'out_norm': a feed-forward and its norm come together")
+        for n in (self.mixer_norm, self.ffn_norm):
+            if n is not None and not hasattr(n, "add"):
+                raise ValueError("block 'out_norm' needs norms that add a sublayer's normalised output to the stream (kind 'rms_out')")
+
+    @staticmethod
+    def _settle(ctx, x, delta) -> None:
+        """What the block before left to be added to x is added now (this block's sublayers read x itself)."""
+        if delta is None:
+            return
+        if isinstance(delta, PreparedRows):
+            return                                  # the product that made them has completed x already
+        for part in (delta if delta.dim() == 3 else delta.unsqueeze(0)):
+            ops.residual_add(x, part.contiguous())
+        ctx.rounded_stream = None
+
+    @staticmethod
+    def _reads(ctx, x):
+        """What a sublayer reads: x in 32-bit, its rounding in bfloat16 (made here if nobody left one)."""
+        if ctx.dtype == torch.float32:
+            return x
+        r = ctx.rounded_stream
+        if r is None or r.shape != x.shape:
+            r = ops.round_rows(x)
+        return r
+
+    def _sublayer(self, ctx, x, norm, run) -> None:
+        h = self._reads(ctx, x)
+        y = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+        ctx.fresh_residual, ctx.norm_ahead = True, None
+        try:
+            left = run(h, y)
+            if left is None and ctx.fresh_residual and x.shape[0]:
+                raise RuntimeError("block 'out_norm': the sublayer did not hand over its output (parts.linear.matmul_into_residual)")
+        finally:
+            ctx.fresh_residual = False
+        rounded = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device) if ctx.dtype == torch.bfloat16 else None
+        norm.add(ctx, x, y if left is None else left, rounded)
+        ctx.rounded_stream = rounded
+
+    def forward(self, ctx, x, cache, delta=None):
+        self._settle(ctx, x, delta)
+        self._sublayer(ctx, x, self.mixer_norm, lambda h, y: self.mixer.forward(ctx, h, y, cache))
+        if self.ffn is not None:
+            self._sublayer(ctx, x, self.ffn_norm, lambda h, y: self.ffn.forward(ctx, h, y))
+        return None
+
+
 register_part("block", "prenorm", PreNormBlock)
+register_part("block", "out_norm", OutNormBlock)
 register_part("block", "prenorm_mixer", PreNormMixerBlock)

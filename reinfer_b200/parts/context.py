@@ -62,6 +62,13 @@ class StepContext:
     # None: nobody asked.  `norm_after_block`: the same for the last part of a block, set by the loop over the layers.
     norm_ahead: Optional[object] = None
     norm_after_block: Optional[object] = None
+    # A block whose sublayers read the residual stream itself hands the stream's bfloat16 rounding to the block behind
+    # it here (made by the kernel that last wrote the stream; None: nobody made one).  The model's loop drops it
+    # before a block that does not say `reads_rounded_stream`, since such a block changes the stream unseen.
+    rounded_stream: Optional[torch.Tensor] = None
+    # The tensor a part was handed as `residual` holds nothing yet: the first product into it stores instead of
+    # adding and clears this (`matmul_into_residual`).  Set by a block that wants a sublayer's output by itself.
+    fresh_residual: bool = False
 
     def empty(self, shape, dtype=None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)

@@ -19,8 +19,11 @@ class Embedding(Part):
     the token table (a tied output head takes the table under this name)."""
 
     def __init__(self, vocab: int, hidden: int, positions: int = 0, table_name: str = "weight",
-                 positions_name: str = "positions.weight"):
+                 positions_name: str = "positions.weight", scale: float = 1.0, rounded_copy: bool = False):
+        """scale: a factor on the rows.  rounded_copy: in bfloat16 the gather also leaves the rows rounded, as
+        `ctx.rounded_stream`, for a first block whose sublayers read the stream itself."""
         self.vocab, self.hidden, self.positions = int(vocab), int(hidden), int(positions)
+        self.scale, self.rounded_copy = float(scale), bool(rounded_copy)
         self.table_name, self.positions_name = str(table_name), str(positions_name)
         self.weight = None
         self.pos_weight = None
@@ -45,8 +48,12 @@ class Embedding(Part):
 
     def forward(self, ctx) -> torch.Tensor:
         x = torch.empty((ctx.n_tokens, self.hidden), dtype=torch.float32, device=ctx.device)
+        rounded = None
+        if self.rounded_copy and ctx.dtype == torch.bfloat16:
+            rounded = torch.empty((ctx.n_tokens, self.hidden), dtype=torch.bfloat16, device=ctx.device)
         ops.embed_gather(self.weight, ctx.token_ids, x, ctx.slot_token, ctx.entry_slot, ctx.tok_entry,
-                         pos_table=self.pos_weight, positions=ctx.positions)
+                         pos_table=self.pos_weight, positions=ctx.positions, scale=self.scale, rounded=rounded)
+        ctx.rounded_stream = rounded
         return x
 
 
@@ -54,18 +61,21 @@ class LMHead(Part):
     """`tied`: the embedding table is the output matrix; the model hands it over in bind()
     under the local name 'weight' either way."""
 
-    def __init__(self, vocab: int, hidden: int, tied: bool = False, fallback: str = "", softcap: float = 0.0):
+    def __init__(self, vocab: int, hidden: int, tied: bool = False, fallback: str = "", softcap: float = 0.0,
+                 weight_name: str = "weight"):
+        """weight_name: the local name of an untied output matrix ("" where the part's prefix is the whole name)."""
         self.vocab, self.hidden, self.tied, self.fallback = int(vocab), int(hidden), bool(tied), fallback
+        self.weight_name = str(weight_name)
         self.softcap = float(softcap or 0.0)        # > 0: logits <- cap * tanh(logits / cap)
         self.weight = None
 
     def param_specs(self):
         if self.tied:
             return {}
-        return {"weight": ParamSpec((self.vocab, self.hidden), optional=bool(self.fallback), fallback=self.fallback)}
+        return {self.weight_name: ParamSpec((self.vocab, self.hidden), optional=bool(self.fallback), fallback=self.fallback)}
 
     def bind(self, tensors):
-        self.weight = tensors["weight"]
+        self.weight = tensors["weight" if self.tied else self.weight_name]
 
     def forward(self, ctx, xn_rows: torch.Tensor) -> torch.Tensor:
         logits = matmul(ctx, xn_rows, self.weight, out_dtype=torch.float32)

@@ -59,15 +59,29 @@ def matmul_into_residual(ctx, a: torch.Tensor, w: torch.Tensor, residual: torch.
     added to the residual here and None is returned.
 
     Where a block named the norm that reads the residual next (ctx.norm_ahead) and that norm can have its rows made
-    by the product itself, the product adds into the residual and this returns those rows (PreparedRows)."""
+    by the product itself, the product adds into the residual and this returns those rows (PreparedRows).
+
+    Where a block set ctx.fresh_residual (the tensor it handed as `residual` holds nothing yet), the first product
+    stores into it instead of adding, or leaves its partial sums as the whole output, and the mark is cleared."""
+    fresh = getattr(ctx, "fresh_residual", False)
     norm = getattr(ctx, "norm_ahead", None)
-    if norm is not None and a.shape[0] and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+    if norm is not None and not fresh and a.shape[0] and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         made = norm.prepared_by(ctx, a, w, residual)
         if made is not None:
             return made
     if getattr(ctx, "defer_residual", False):
         parts = ops.gemm_bf16_partials(a, w) if a.shape[0] else None
         if parts is not None:
+            if fresh:
+                ctx.fresh_residual = False          # the stack is the whole output so far; `residual` stays unused
             return parts
+    if fresh:
+        # `residual` holds nothing yet (a block that wants this sublayer's output by itself): store, and what
+        # comes after adds
+        ctx.fresh_residual = False
+        if a.shape[0] == 0:
+            return None
+        matmul(ctx, a, w, out=residual, accumulate=False)
+        return None
     matmul(ctx, a, w, out=residual, accumulate=True)
     return None

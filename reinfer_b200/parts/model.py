@@ -169,6 +169,8 @@ class Model:
             delta = None                        # what a block left to be added to x by the norm that reads x next
             for n, (i, key) in enumerate(self.run):
                 block = self.layers[i].block
+                if not getattr(block, "reads_rounded_stream", False):
+                    ctx.rounded_stream = None       # this block changes the stream without leaving its rounding
                 if self._norms_add_partial_sums:
                     # the block that runs next may let this one's last product do its first norm's work
                     nxt = self.layers[self.run[n + 1][0]].block if n + 1 < len(self.run) else None
@@ -178,6 +180,7 @@ class Model:
                 else:
                     block.forward(ctx, x, ctx.layer_caches[key])
             ctx.norm_after_block = None
+            ctx.rounded_stream = None
             if want_rows is None or want_rows.numel() == 0:
                 return None                     # (a sum still owed to x is dropped with x)
             xn = self.final_norm.forward(ctx, x, delta=delta, row_idx=want_rows)

@@ -1,0 +1,69 @@
+"""A mixture of small feed-forward experts.  Each token uses `top` of `experts + identity` choices:
+
+    s      = softmax(router(x))                  over all choices, 32-bit
+    chosen = the `top` largest of s + correction (the correction steers the choice only)
+    out    = sum over the chosen e of s[e] * expert_e(x)       (the weights are not renormalised)
+
+An expert is down(act(up(x))) with act = relu(.)^2 and no biases; the last `identity` choices are experts that
+hand their input back unchanged and have no tensors.
+
+The experts' up matrices are stacked by rows at load and their down matrices side by side, and the router's choice
+is kept dense (gates [T, experts], zero where an expert was not chosen): one product makes every expert's inner
+activations, the activation kernel multiplies each by its token's gate, and one product with the stacked down
+matrices is then the weighted sum over the chosen experts, an expert that was not chosen adding exact zeros.  A
+token's result never depends on what else is in the batch.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..weights.params import ParamSpec
+from .base import FeedForward, register_part
+from .linear import matmul, matmul_into_residual
+
+
+class ExpertMixture(FeedForward):
+    def __init__(self, hidden: int, experts: int, top: int, inner: int, identity: int = 0,
+                 expert_names=("e{}.up", "e{}.down"), router_name: str = "router", correction_name: str = "correction"):
+        self.hidden, self.E, self.I, self.top, self.ff = int(hidden), int(experts), int(identity), int(top), int(inner)
+        if self.E < 1 or self.I < 0 or not 1 <= self.top <= self.E + self.I:
+            raise ValueError(f"expert mixture: {self.E} experts, {self.I} identity experts, top {self.top}")
+        self.up_name, self.down_name = expert_names
+        self.router_name, self.correction_name = router_name, correction_name
+        self.w_up = self.w_down = self.w_router = self.correction = None
+
+    def param_specs(self):
+        h, n = self.hidden, self.E + self.I
+        out = {self.router_name: ParamSpec((n, h), std=0.1), self.correction_name: ParamSpec((n,), std=0.02)}
+        for e in range(self.E):
+            out[self.up_name.format(e)] = ParamSpec((self.ff, h))
+            out[self.down_name.format(e)] = ParamSpec((h, self.ff))
+        return out
+
+    def bind(self, t):
+        ups = [t[self.up_name.format(e)] for e in range(self.E)]
+        downs = [t[self.down_name.format(e)] for e in range(self.E)]
+        if len({m.dtype for m in ups + downs}) > 1:
+            ups, downs = [m.float() for m in ups], [m.float() for m in downs]
+        self.w_up = torch.cat(ups, dim=0).contiguous()                  # [E * ff, h]
+        self.w_down = torch.cat(downs, dim=1).contiguous()              # [h, E * ff]
+        self.w_router = t[self.router_name]
+        self.correction = t[self.correction_name].float().contiguous()
+
+    def forward(self, ctx, xn, residual):
+        T = xn.shape[0]
+        z = torch.empty((T, self.E + self.I), dtype=torch.float32, device=xn.device)
+        ops.gemm_ref(xn, self.w_router, z)                               # the router in 32-bit, one chain per output
+        gates, ident = ops.moe_route(z, self.correction, self.E, self.top)
+        act = ops.relu2_gate(matmul(ctx, xn, self.w_up), gates, self.ff)
+        if ident is not None:
+            ctx.norm_ahead = None           # the stream is not complete behind the down product: nobody's rows can be made there
+        left = matmul_into_residual(ctx, act, self.w_down, residual)
+        if ident is not None and T:
+            # the identity experts' share: the token's own row times the sum of their chosen scores
+            ops.rows_axpy(residual if left is None else left[0], ident, xn)
+        return left
+
+
+register_part("ffn", "expert_mixture", ExpertMixture)

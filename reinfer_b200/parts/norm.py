@@ -14,15 +14,16 @@ class RMSNorm(Norm):
     adds_partial_sums = True            # delta may be a stack [S, rows, width] of partial sums
     leaves_row_scale = True             # forward(..., scaled_ok=True) may return a RowScaled
 
-    def __init__(self, width: int, eps: float):
-        self.width, self.eps = int(width), float(eps)
+    def __init__(self, width: int, eps: float, weight_name: str = "weight"):
+        """weight_name: the local name of the weight ("" where the part's prefix is the tensor's whole name)."""
+        self.width, self.eps, self.weight_name = int(width), float(eps), str(weight_name)
         self.weight = None
 
     def param_specs(self):
-        return {"weight": ParamSpec((self.width,), init="norm")}
+        return {self.weight_name: ParamSpec((self.width,), init="norm")}
 
     def bind(self, tensors):
-        self.weight = tensors["weight"]
+        self.weight = tensors[self.weight_name]
 
     def prepared_by(self, ctx, a, w, residual):
         """residual += a w^T by a product that also makes this norm's rows of the new residual (a decode step's few
@@ -52,4 +53,29 @@ class RMSNorm(Norm):
         return out
 
 
+class ResidualOutNorm(Norm):
+    """The norm of a layer that normalises what a sublayer puts OUT, not what it reads:
+        x += mult * y / sqrt(mean(y^2) + eps) * w
+    in one kernel, 32-bit.  y is the sublayer's output as float32 rows, or the stack of partial sums its last
+    product left.  `add` can leave the new x once more, rounded to bfloat16, for the sublayer that reads it next."""
+    adds_partial_sums = True
+
+    def __init__(self, width: int, eps: float, mult: float = 1.0, weight_name: str = "weight"):
+        self.width, self.eps, self.mult, self.weight_name = int(width), float(eps), float(mult), str(weight_name)
+        self.weight = None
+
+    def param_specs(self):
+        return {self.weight_name: ParamSpec((self.width,), init="norm")}
+
+    def bind(self, tensors):
+        self.weight = tensors[self.weight_name]
+
+    def add(self, ctx, x, y, rounded=None) -> None:
+        ops.residual_outnorm(x, y, self.weight, self.eps, self.mult, rounded=rounded)
+
+    def forward(self, ctx, x, out=None, delta=None, row_idx=None):
+        raise TypeError("an output norm has no rows to hand on: the block calls add(ctx, x, y)")
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "rms_out", ResidualOutNorm)
