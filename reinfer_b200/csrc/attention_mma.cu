@@ -20,7 +20,11 @@
 // Two optional extras serve attention that is local to chunks of positions and has no rotation: a chunk mask (a row
 // sees only the keys from the start of its own chunk of `chunk` positions, counted from position 0) and a penalty on
 // distance per query head, score -= r1[h] ln(1 + r2[h] (i - j)), added in the exponent's base-2 domain as
-// r1 log2(1 + r2 (i - j)); and a factor on the output.  Without them the kernels are what they were.
+// r1 log2(1 + r2 (i - j)); and a factor on the output.  Two more serve attention with a learned bias by distance and
+// value heads of their own size: a float table bias[min(i - j, rows - 1)][head] that is added to the scaled score
+// (the last row stands for every greater distance), and dv != d (a page is then [K: KH x page x d | V: KH x page x
+// dv]; the tiles are as wide as the larger of the two, the narrower zero-filled).  Without them the kernels are
+// what they were.
 //
 // Head sizes: the template is instantiated for 32, 64, 128 and 256; a head size that is a
 // multiple of 8 below the next instance is zero-padded in shared memory.
@@ -50,6 +54,9 @@ struct FaArgs {
     const float* r1;                   // [QH] distance penalty (null: none)
     const float* r2;
     float out_scale;
+    int dv;                            // the value heads' size (= d unless the layer says otherwise)
+    const float* bias;                 // [bias_rows, QH] added to the scaled scores by distance (null: none)
+    int bias_rows;
 };
 
 // ---------------------------------------------------------------- small PTX wrappers
@@ -97,27 +104,31 @@ __device__ __forceinline__ void fa_load_tile(unsigned char* stage, const FaArgs&
     constexpr int RPI = FA_THREADS / CPR;                     // rows per pass over the tile
     static_assert(FA_THREADS % CPR == 0 && FA_BN % RPI == 0, "tile shape");
     const int c = threadIdx.x % CPR, r0 = threadIdx.x / CPR;
-    const bool col_ok = c * 8 < a.d;
-    const size_t head_stride = (size_t)a.page_size * a.d;
-    const size_t page_stride = 2 * (size_t)a.KH * head_stride;
-    const bf16* base = a.cache + (size_t)kh * head_stride + c * 8;
-    const size_t v_off = (size_t)a.KH * head_stride;
+    const bool kcol_ok = c * 8 < a.d, vcol_ok = c * 8 < a.dv;
+    const size_t head_stride = (size_t)a.page_size * a.d, vhead_stride = (size_t)a.page_size * a.dv;
+    const size_t page_stride = (size_t)a.KH * (head_stride + vhead_stride);
+    const bf16* kbase = a.cache + (size_t)kh * head_stride + c * 8;
+    const bf16* vbase = a.cache + (size_t)a.KH * head_stride + (size_t)kh * vhead_stride + c * 8;
     unsigned char* dst0 = stage + r0 * FaSmem<D>::STRIDE + c * 16;
 #pragma unroll
     for (int i = 0; i < FA_BN / RPI; ++i) {
         const int key = k0 + r0 + i * RPI;
-        const bf16* src = a.cache;
-        int bytes = 0;
-        if (col_ok && key < kv_end) {
+        const bf16* ksrc = a.cache;
+        const bf16* vsrc = a.cache;
+        int kbytes = 0, vbytes = 0;
+        if (key < kv_end) {
             int pi, off;
             if (a.page_shift >= 0) { pi = key >> a.page_shift; off = key & (a.page_size - 1); }
             else { pi = key / a.page_size; off = key - pi * a.page_size; }
             const int page = pi < a.max_pages ? bt[pi] : -1;
-            if (page >= 0) { src = base + (size_t)page * page_stride + (size_t)off * a.d; bytes = 16; }
+            if (page >= 0) {
+                if (kcol_ok) { ksrc = kbase + (size_t)page * page_stride + (size_t)off * a.d; kbytes = 16; }
+                if (vcol_ok) { vsrc = vbase + (size_t)page * page_stride + (size_t)off * a.dv; vbytes = 16; }
+            }
         }
         unsigned char* dst = dst0 + i * RPI * FaSmem<D>::STRIDE;
-        cp_async16(dst, src, bytes);
-        cp_async16(dst + FaSmem<D>::TILE, bytes ? src + v_off : src, bytes);
+        cp_async16(dst, ksrc, kbytes);
+        cp_async16(dst + FaSmem<D>::TILE, vsrc, vbytes);
     }
 }
 
@@ -128,7 +139,8 @@ template <int D, int NT>
 __device__ __forceinline__ void fa_tile(const unsigned char* sQ, const unsigned char* sK, const unsigned char* sV,
                                         int koff, int k0_abs, int pos0, int pos1, int lo0, int lo1, float scale_log2,
                                         float (&o)[D / 8][4], float (&m)[2], float (&l)[2],
-                                        bool pen = false, float pa0 = 0.0f, float pb0 = 0.0f, float pa1 = 0.0f, float pb1 = 0.0f) {
+                                        bool pen = false, float pa0 = 0.0f, float pb0 = 0.0f, float pa1 = 0.0f, float pb1 = 0.0f,
+                                        const float* bias0 = nullptr, const float* bias1 = nullptr, int bias_stride = 0, int bias_last = 0) {
     constexpr int STRIDE = FaSmem<D>::STRIDE;
     const int lane = threadIdx.x & 31;
     float s[NT][4];
@@ -157,6 +169,16 @@ __device__ __forceinline__ void fa_tile(const unsigned char* sQ, const unsigned 
             v1 = fmaf(-pa0, __log2f(fmaf(pb0, (float)(pos0 - key - 1), 1.0f)), v1);
             v2 = fmaf(-pa1, __log2f(fmaf(pb1, (float)(pos1 - key), 1.0f)), v2);
             v3 = fmaf(-pa1, __log2f(fmaf(pb1, (float)(pos1 - key - 1), 1.0f)), v3);
+        }
+        if (bias0) {                                           // the learned bias by distance, in the exponent's base-2 domain
+            constexpr float LOG2E = 1.4426950408889634f;
+            v0 = fmaf(bias0[(size_t)min(max(pos0 - key, 0), bias_last) * bias_stride], LOG2E, v0);
+            v1 = fmaf(bias0[(size_t)min(max(pos0 - key - 1, 0), bias_last) * bias_stride], LOG2E, v1);
+        }
+        if (bias1) {
+            constexpr float LOG2E = 1.4426950408889634f;
+            v2 = fmaf(bias1[(size_t)min(max(pos1 - key, 0), bias_last) * bias_stride], LOG2E, v2);
+            v3 = fmaf(bias1[(size_t)min(max(pos1 - key - 1, 0), bias_last) * bias_stride], LOG2E, v3);
         }
         s[j][0] = (key >= lo0 && key <= pos0) ? v0 : -INFINITY;
         s[j][1] = (key + 1 >= lo0 && key + 1 <= pos0) ? v1 : -INFINITY;
@@ -256,6 +278,8 @@ fa_prefill_kernel(const FaArgs a) {
     const bool pen = a.r1 != nullptr;
     const int hd0 = head0 + r0 % a.Gc, hd1 = head0 + r1 % a.Gc;
     const float pa0 = pen ? a.r1[hd0] : 0.0f, pb0 = pen ? a.r2[hd0] : 0.0f, pa1 = pen ? a.r1[hd1] : 0.0f, pb1 = pen ? a.r2[hd1] : 0.0f;
+    const float* bias0 = a.bias ? a.bias + hd0 : nullptr;
+    const float* bias1 = a.bias ? a.bias + hd1 : nullptr;
     // keys beyond the last row of this WARP are masked for all its rows: the warp may stop early
     const int warp_last_tok = min(n_tok - 1, (warp * 16 + 15) / a.Gc);
     const int warp_t_end = (warp * 16) / a.Gc < n_tok ? (start_pos + q0 + warp_last_tok) / FA_BN + 1 : 0;
@@ -276,7 +300,8 @@ fa_prefill_kernel(const FaArgs a) {
         if (t < warp_t_end) {
             const unsigned char* sK = stages + buf * FaSmem<D>::STAGE;
             fa_tile<D, FA_BN / 8>(sQ + warp * 16 * FaSmem<D>::STRIDE, sK, sK + FaSmem<D>::TILE, 0, t * FA_BN,
-                                  pos0, pos1, lo0, lo1, a.scale_log2, o, m, l, pen, pa0, pb0, pa1, pb1);
+                                  pos0, pos1, lo0, lo1, a.scale_log2, o, m, l, pen, pa0, pb0, pa1, pb1,
+                                  bias0, bias1, a.QH, a.bias_rows - 1);
         }
     }
     cp_async_wait<0>();
@@ -291,11 +316,11 @@ fa_prefill_kernel(const FaArgs a) {
 #pragma unroll
     for (int j = 0; j < D / 8; ++j) {
         const int dim = j * 8 + 2 * (lane & 3);
-        if (dim >= a.d) continue;
+        if (dim >= a.dv) continue;
         if (ti0 < n_tok)
-            *reinterpret_cast<uint32_t*>(a.out + ((size_t)(tok_base + ti0) * a.QH + head0 + r0 % a.Gc) * a.d + dim) = pack_bf16(o[j][0] * inv0, o[j][1] * inv0);
+            *reinterpret_cast<uint32_t*>(a.out + ((size_t)(tok_base + ti0) * a.QH + head0 + r0 % a.Gc) * a.dv + dim) = pack_bf16(o[j][0] * inv0, o[j][1] * inv0);
         if (ti1 < n_tok)
-            *reinterpret_cast<uint32_t*>(a.out + ((size_t)(tok_base + ti1) * a.QH + head0 + r1 % a.Gc) * a.d + dim) = pack_bf16(o[j][2] * inv1, o[j][3] * inv1);
+            *reinterpret_cast<uint32_t*>(a.out + ((size_t)(tok_base + ti1) * a.QH + head0 + r1 % a.Gc) * a.dv + dim) = pack_bf16(o[j][2] * inv1, o[j][3] * inv1);
     }
 }
 
@@ -328,6 +353,8 @@ fa_decode_kernel(const FaArgs a) {
     const bool pen = a.r1 != nullptr;
     const float pa0 = (pen && row0 < a.Gc) ? a.r1[head0 + row0] : 0.0f, pb0 = (pen && row0 < a.Gc) ? a.r2[head0 + row0] : 0.0f;
     const float pa1 = (pen && row0 + 8 < a.Gc) ? a.r1[head0 + row0 + 8] : 0.0f, pb1 = (pen && row0 + 8 < a.Gc) ? a.r2[head0 + row0 + 8] : 0.0f;
+    const float* bias0 = (a.bias && row0 < a.Gc) ? a.bias + head0 + row0 : nullptr;
+    const float* bias1 = (a.bias && row0 + 8 < a.Gc) ? a.bias + head0 + row0 + 8 : nullptr;
     float o[D / 8][4];
 #pragma unroll
     for (int j = 0; j < D / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f; }
@@ -346,7 +373,8 @@ fa_decode_kernel(const FaArgs a) {
             fa_load_tile<D>(stages + ((it + NST - 1) % NST) * FaSmem<D>::STAGE, a, bt, kh, (t + NST - 1) * FA_BN, kv_end);
         cp_async_commit();
         const unsigned char* sK = stages + (it % NST) * FaSmem<D>::STAGE;
-        fa_tile<D, 2>(sQ, sK, sK + FaSmem<D>::TILE, warp * 16, t * FA_BN, pos0, pos1, lo, lo, a.scale_log2, o, m, l, pen, pa0, pb0, pa1, pb1);
+        fa_tile<D, 2>(sQ, sK, sK + FaSmem<D>::TILE, warp * 16, t * FA_BN, pos0, pos1, lo, lo, a.scale_log2, o, m, l, pen, pa0, pb0, pa1, pb1,
+                      bias0, bias1, a.QH, a.bias_rows - 1);
     }
     cp_async_wait<0>();
     __syncthreads();                                           // the stages are free: reuse them for the merge
@@ -369,8 +397,8 @@ fa_decode_kernel(const FaArgs a) {
         sL[warp * 16 + row0] = l[0]; sL[warp * 16 + row0 + 8] = l[1];
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < a.Gc * a.d; i += FA_THREADS) {
-        const int row = i / a.d, dim = i % a.d;
+    for (int i = threadIdx.x; i < a.Gc * a.dv; i += FA_THREADS) {
+        const int row = i / a.dv, dim = i % a.dv;
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < FA_WARPS; ++w) M = fmaxf(M, sM[w * 16 + row]);
@@ -386,10 +414,10 @@ fa_decode_kernel(const FaArgs a) {
         const float val = L > 0.0f ? O / L * a.out_scale : 0.0f;
         const int head = head0 + row;
         if (a.n_splits == 1) {
-            a.out[((size_t)tok * a.QH + head) * a.d + dim] = __float2bfloat16_rn(val);
+            a.out[((size_t)tok * a.QH + head) * a.dv + dim] = __float2bfloat16_rn(val);
         } else {
             const size_t pi = ((size_t)(tok - a.cu_q[a.first_entry]) * a.QH + head) * a.n_splits + split;
-            a.part_o[pi * a.d + dim] = val;
+            a.part_o[pi * a.dv + dim] = val;
             if (dim == 0) a.part_lse[pi] = L > 0.0f ? M + log2f(L) : -INFINITY;
         }
     }
@@ -451,9 +479,11 @@ static int fa_launch_decode(const FaArgs& a, cudaStream_t s) {
     return rb_launch(fa_decode_kernel<D, NST>, dim3(a.n_entries, a.KH * a.chunks, a.n_splits), dim3(FA_THREADS), smem, s, a);
 }
 
-static int fa_check(int QH, int KH, int d, int page_size, int max_pages) {
+static int fa_check(int QH, int KH, int d, int page_size, int max_pages, int dv = 0, const float* bias = nullptr, int bias_rows = 0) {
     if (QH <= 0 || KH <= 0 || QH % KH) RB_REFUSE("attention: %d query heads over %d kv heads", QH, KH);
     if (d <= 0 || d % 8 || d > 256) RB_REFUSE("attention (tensor cores): head_dim %d is not a multiple of 8 up to 256", d);
+    if (dv < 0 || dv % 8 || dv > 256) RB_REFUSE("attention (tensor cores): value head size %d is not a multiple of 8 up to 256", dv);
+    if (bias && bias_rows <= 0) RB_REFUSE("attention: a distance bias of %d rows", bias_rows);
     if (page_size <= 0 || max_pages <= 0) RB_REFUSE("attention: page_size %d max_pages %d", page_size, max_pages);
     return 0;
 }
@@ -465,31 +495,34 @@ extern "C" int rb_fa_group_chunk(int G) { return fa_group_chunk(G); }
 extern "C" int rb_fa_prefill(const void* q, const void* cache, const int* block_table, const int* cu_q, const int* kv_len,
                              void* out, int first_entry, int n_entries, int n_tiles, int QH, int KH, int d, int page_size,
                              int max_pages, int window, float scale, int chunk, const float* r1, const float* r2, float out_scale,
-                             void* stream) {
+                             int dv, const float* bias, int bias_rows, void* stream) {
     if (n_entries <= 0 || n_tiles <= 0) return 0;
-    if (fa_check(QH, KH, d, page_size, max_pages)) return -1;
+    if (fa_check(QH, KH, d, page_size, max_pages, dv, bias, bias_rows)) return -1;
     if (chunk < 0 || (r1 == nullptr) != (r2 == nullptr)) RB_REFUSE("attention: chunk %d, or half a distance penalty", chunk);
     FaArgs a{};
     a.chunk = chunk; a.r1 = r1; a.r2 = r2; a.out_scale = out_scale;
+    a.dv = dv > 0 ? dv : d; a.bias = bias; a.bias_rows = bias_rows;
     a.q = (const bf16*)q; a.cache = (const bf16*)cache; a.block_table = block_table; a.cu_q = cu_q; a.kv_len = kv_len;
     a.out = (bf16*)out; a.QH = QH; a.KH = KH; a.d = d; a.page_size = page_size; a.page_shift = fa_shift(page_size); a.max_pages = max_pages; a.window = window;
     a.Gc = fa_group_chunk(QH / KH); a.chunks = (QH / KH) / a.Gc; a.first_entry = first_entry; a.n_entries = n_entries;
     a.n_splits = 1; a.scale_log2 = scale * 1.4426950408889634f;
     cudaStream_t s = (cudaStream_t)stream;
-    if (d <= 32) return fa_launch_prefill<32>(a, n_tiles, s);
-    if (d <= 64) return fa_launch_prefill<64>(a, n_tiles, s);
-    if (d <= 128) return fa_launch_prefill<128>(a, n_tiles, s);
+    const int wide = a.dv > d ? a.dv : d;                     // the tiles' width serves both sizes
+    if (wide <= 32) return fa_launch_prefill<32>(a, n_tiles, s);
+    if (wide <= 64) return fa_launch_prefill<64>(a, n_tiles, s);
+    if (wide <= 128) return fa_launch_prefill<128>(a, n_tiles, s);
     return fa_launch_prefill<256>(a, n_tiles, s);
 }
 
 // Decode entries [first_entry, first_entry + n_entries): one token each.  With n_splits > 1 the scratch
-// part_o [n_entries*QH*n_splits*d] and part_lse [n_entries*QH*n_splits] (floats) must be given.
+// part_o [n_entries*QH*n_splits*dv] and part_lse [n_entries*QH*n_splits] (floats) must be given.
 extern "C" int rb_fa_decode(const void* q, const void* cache, const int* block_table, const int* cu_q, const int* kv_len,
                             void* out, float* part_o, float* part_lse, int first_entry, int n_entries, int first_tok,
                             int n_splits, int QH, int KH, int d, int page_size, int max_pages, int window, float scale,
-                            int chunk, const float* r1, const float* r2, float out_scale, void* stream) {
+                            int chunk, const float* r1, const float* r2, float out_scale, int dv, const float* bias,
+                            int bias_rows, void* stream) {
     if (n_entries <= 0) return 0;
-    if (fa_check(QH, KH, d, page_size, max_pages)) return -1;
+    if (fa_check(QH, KH, d, page_size, max_pages, dv, bias, bias_rows)) return -1;
     if (chunk < 0 || (r1 == nullptr) != (r2 == nullptr)) RB_REFUSE("attention: chunk %d, or half a distance penalty", chunk);
     if (n_splits < 1 || n_splits > 65535) RB_REFUSE("attention: %d splits", n_splits);
     if (n_splits > 1 && (!part_o || !part_lse)) RB_REFUSE("attention: split decoding needs its scratch");
@@ -497,16 +530,18 @@ extern "C" int rb_fa_decode(const void* q, const void* cache, const int* block_t
     a.q = (const bf16*)q; a.cache = (const bf16*)cache; a.block_table = block_table; a.cu_q = cu_q; a.kv_len = kv_len;
     a.out = (bf16*)out; a.part_o = part_o; a.part_lse = part_lse;
     a.chunk = chunk; a.r1 = r1; a.r2 = r2; a.out_scale = out_scale;
+    a.dv = dv > 0 ? dv : d; a.bias = bias; a.bias_rows = bias_rows;
     a.QH = QH; a.KH = KH; a.d = d; a.page_size = page_size; a.page_shift = fa_shift(page_size); a.max_pages = max_pages; a.window = window;
     a.Gc = fa_group_chunk(QH / KH); a.chunks = (QH / KH) / a.Gc; a.first_entry = first_entry; a.n_entries = n_entries;
     a.n_splits = n_splits; a.scale_log2 = scale * 1.4426950408889634f;
     cudaStream_t s = (cudaStream_t)stream;
     int rc;
-    if (d <= 32) rc = fa_launch_decode<32, 3>(a, s);
-    else if (d <= 64) rc = fa_launch_decode<64, 3>(a, s);
-    else if (d <= 128) rc = fa_launch_decode<128, 3>(a, s);
+    const int wide = a.dv > d ? a.dv : d;
+    if (wide <= 32) rc = fa_launch_decode<32, 3>(a, s);
+    else if (wide <= 64) rc = fa_launch_decode<64, 3>(a, s);
+    else if (wide <= 128) rc = fa_launch_decode<128, 3>(a, s);
     else rc = fa_launch_decode<256, 2>(a, s);
     if (rc || n_splits == 1) return rc;
     return rb_launch(fa_merge_kernel, dim3(n_entries, QH), dim3(128), 0, s, (const float*)part_o, (const float*)part_lse,
-                     (bf16*)out, first_tok, QH, d, n_splits);
+                     (bf16*)out, first_tok, QH, a.dv, n_splits);
 }

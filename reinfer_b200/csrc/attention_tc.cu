@@ -77,6 +77,10 @@ struct FcArgs {
     const float* r1;
     const float* r2;
     float out_scale;
+    // A learned bias by distance: score += bias[min(i - j, bias_last)][h] (a float table [bias_last + 1, QH] in units of
+    // the scaled score; null: none).  Its last row stands for every greater distance.
+    const float* bias;
+    int bias_last;
 };
 
 struct FcShared {
@@ -390,6 +394,11 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
         // the distance penalty of this row's head, in units of the raw score (the scale is applied to the difference)
         const bool pen = a.r1 != nullptr;
         const float pen_a = pen ? a.r1[head0 + row % a.Gc] / a.scale_log2 : 0.0f, pen_b = pen ? a.r2[head0 + row % a.Gc] : 0.0f;
+        // the bias by distance of this row's head, in units of the raw score like the penalty; a tile whose keys all lie
+        // at least bias_last behind the row gets one constant
+        const float* brow = a.bias ? a.bias + head0 + row % a.Gc : nullptr;
+        const float bias_unit = 1.4426950408889634f / a.scale_log2;
+        const float bias_far = brow ? brow[(size_t)a.bias_last * a.QH] * bias_unit : 0.0f;
         // m: the maximum that P and O are scaled to (it follows the true maximum only in steps larger than
         // FC_RESCALE, so that O can stay in tensor memory and be accumulated by the MMA itself); l: the sum in that scale
         float m = -INFINITY, l = 0.0f;
@@ -435,6 +444,19 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
 #pragma unroll
                 for (int j = 0; j < FC_BN; ++j)
                     sr[j] = __float_as_uint(fmaf(-pen_a, __log2f(fmaf(pen_b, dist0 - (float)j, 1.0f)), __uint_as_float(sr[j])));
+            }
+            if (brow) {
+                const int d0 = pos - k0;                           // distance of the tile's first key (a dead row: below zero)
+                if (d0 - (FC_BN - 1) >= a.bias_last) {
+#pragma unroll
+                    for (int j = 0; j < FC_BN; ++j) sr[j] = __float_as_uint(__uint_as_float(sr[j]) + bias_far);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < FC_BN; ++j) {
+                        const int dist = min(max(d0 - j, 0), a.bias_last);
+                        sr[j] = __float_as_uint(fmaf(brow[(size_t)dist * a.QH], bias_unit, __uint_as_float(sr[j])));
+                    }
+                }
             }
             if (edge) {
 #pragma unroll
@@ -581,9 +603,10 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
 extern "C" int rb_fa_prefill_tc(const void* q, const void* cache, long long num_pages, const int* block_table, const int* cu_q,
                                 const int* kv_len, void* out, int first_entry, int n_entries, int n_tiles, int QH, int KH, int d,
                                 int page_size, int max_pages, int window, float scale, int chunk, const float* r1, const float* r2,
-                                float out_scale, void* stream) {
+                                float out_scale, const float* bias, int bias_rows, void* stream) {
     if (n_entries <= 0 || n_tiles <= 0) return 0;
     if (QH <= 0 || KH <= 0 || QH % KH) RB_REFUSE("attention: %d query heads over %d kv heads", QH, KH);
+    if (bias && bias_rows <= 0) RB_REFUSE("attention: a distance bias of %d rows", bias_rows);
     if (d != FC_D) RB_REFUSE("attention (tcgen05): head_dim %d, only 128 is built", d);
     // a chunk that starts inside a key tile would leave the tile's first keys to pages that may have gone back to the pool
     if (chunk < 0 || chunk % FC_BN || (r1 == nullptr) != (r2 == nullptr)) RB_REFUSE("attention (tcgen05): chunk %d (a multiple of %d), or half a distance penalty", chunk, FC_BN);
@@ -600,6 +623,7 @@ extern "C" int rb_fa_prefill_tc(const void* q, const void* cache, long long num_
     a.chunks = G / a.Gc; a.first_entry = first_entry; a.n_entries = n_entries;
     a.scale_log2 = scale * 1.4426950408889634f;
     a.chunk = chunk; a.r1 = r1; a.r2 = r2; a.out_scale = out_scale;
+    a.bias = bias; a.bias_last = bias_rows - 1;
     CUtensorMap map;
     if (rb_tensor_map_kv_pages(cache, num_pages, KH, page_size, &map)) return -1;
     constexpr size_t smem = (size_t)FC_NST * FC_STAGE + FC_TILES * 4 * FC_QHALF + sizeof(FcShared) + 1024;

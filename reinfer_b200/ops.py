@@ -344,17 +344,18 @@ def _penalty_args(penalty, QH: int):
 
 def fa_decode(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, first_tok: int, n_splits: int,
               QH: int, KH: int, d: int, page_size: int, window: int, scale: float, work=(0.0, 0.0),
-              chunk: int = 0, penalty=None, out_scale: float = 1.0) -> None:
-    """Split-K flash decoding (tensor cores) for entries that bring one token each.  chunk, penalty = (r1, r2) and
-    out_scale as in paged_attention_ref."""
+              chunk: int = 0, penalty=None, out_scale: float = 1.0, dv: int = 0, bias: Optional[torch.Tensor] = None) -> None:
+    """Split-K flash decoding (tensor cores) for entries that bring one token each.  chunk, penalty = (r1, r2),
+    out_scale, dv and bias as in paged_attention_ref."""
     part_o = part_lse = None
     if n_splits > 1:
-        part_o = torch.empty(n_entries * QH * n_splits * d, dtype=torch.float32, device=q.device)
+        part_o = torch.empty(n_entries * QH * n_splits * (dv or d), dtype=torch.float32, device=q.device)
         part_lse = torch.empty(n_entries * QH * n_splits, dtype=torch.float32, device=q.device)
     _check(lib().rb_fa_decode(_p(q), _p(cache), _p(block_table), _p(cu_q), _p(kv_len), _p(out), _p(part_o), _p(part_lse),
                               c_int(first_entry), c_int(n_entries), c_int(first_tok), c_int(n_splits), c_int(QH), c_int(KH),
                               c_int(d), c_int(page_size), c_int(block_table.shape[1]), c_int(window), c_float(scale),
-                              c_int(chunk), *_penalty_args(penalty, QH), c_float(out_scale), _stream()), "fa_decode", *work)
+                              c_int(chunk), *_penalty_args(penalty, QH), c_float(out_scale), c_int(dv), *_bias_args(bias, QH),
+                              _stream()), "fa_decode", *work)
     if n_splits > 1:
         global launches
         launches += 1                      # the merge kernel
@@ -488,17 +489,17 @@ def fa_prefill_tma(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n
 
 def fa_prefill_tc(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, q_lens,
                   QH: int, KH: int, d: int, page_size: int, window: int, scale: float, work=(0.0, 0.0),
-                  chunk: int = 0, penalty=None, out_scale: float = 1.0) -> None:
+                  chunk: int = 0, penalty=None, out_scale: float = 1.0, bias: Optional[torch.Tensor] = None) -> None:
     """Paged causal flash attention on the tcgen05 tensor cores (scores and the weighted sum in tensor memory):
     head size 128, page size a power of two >= 8.  q_lens: the token counts of the entries (host).  chunk (a multiple
-    of 64), penalty = (r1, r2) and out_scale as in paged_attention_ref."""
+    of 64), penalty = (r1, r2), out_scale and bias as in paged_attention_ref."""
     gc = int(lib().rb_fa_prefill_tc_group(c_int(QH), c_int(KH)))
     tpt = int(lib().rb_fa_prefill_tc_rows()) // gc              # tokens that one CTA takes
     n_tiles = sum(-(-int(n) // tpt) for n in q_lens)
     _check(lib().rb_fa_prefill_tc(_p(q), _p(cache), c_longlong(cache.shape[0]), _p(block_table), _p(cu_q), _p(kv_len), _p(out),
                                   c_int(first_entry), c_int(n_entries), c_int(n_tiles), c_int(QH), c_int(KH), c_int(d),
                                   c_int(page_size), c_int(block_table.shape[1]), c_int(window), c_float(scale), c_int(chunk),
-                                  *_penalty_args(penalty, QH), c_float(out_scale), _stream()),
+                                  *_penalty_args(penalty, QH), c_float(out_scale), *_bias_args(bias, QH), _stream()),
            "fa_prefill_tc", *work)
 
 
@@ -508,13 +509,14 @@ def tma_pages(page_size: int) -> bool:
 
 def fa_prefill(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, n_tiles: int,
                QH: int, KH: int, d: int, page_size: int, window: int, scale: float, work=(0.0, 0.0),
-               chunk: int = 0, penalty=None, out_scale: float = 1.0) -> None:
-    """Paged causal flash attention (tensor cores) for entries that bring several tokens.  chunk, penalty = (r1, r2)
-    and out_scale as in paged_attention_ref."""
+               chunk: int = 0, penalty=None, out_scale: float = 1.0, dv: int = 0, bias: Optional[torch.Tensor] = None) -> None:
+    """Paged causal flash attention (tensor cores) for entries that bring several tokens.  chunk, penalty = (r1, r2),
+    out_scale, dv and bias as in paged_attention_ref."""
     _check(lib().rb_fa_prefill(_p(q), _p(cache), _p(block_table), _p(cu_q), _p(kv_len), _p(out), c_int(first_entry),
                                c_int(n_entries), c_int(n_tiles), c_int(QH), c_int(KH), c_int(d), c_int(page_size),
                                c_int(block_table.shape[1]), c_int(window), c_float(scale), c_int(chunk),
-                               *_penalty_args(penalty, QH), c_float(out_scale), _stream()), "fa_prefill", *work)
+                               *_penalty_args(penalty, QH), c_float(out_scale), c_int(dv), *_bias_args(bias, QH), _stream()),
+           "fa_prefill", *work)
 
 
 USE_TMA_ATTENTION = os.environ.get("REINFER_B200_TMA_ATTENTION", "1") != "0"
@@ -1087,8 +1089,44 @@ def biased_attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torc
     """Softmax attention of a step's tokens over their requests' pages, causal or in a sliding window, with a
     learned bias by distance (float32 [rows, QH]; the last row serves every greater distance) added to the scaled
     scores, and value heads of their own size.  q [T, QH, dk], out [T, QH, dv]."""
-    paged_attention_ref(q, cache, group.block_table, ctx.tok_entry, ctx.positions, out, QH, KH, dk, group.page_size, window, scale,
-                        dv=dv, bias=bias)
+    n_dec, E = ctx.n_decode, ctx.n_entries
+    dec_work = pre_work = (0.0, 0.0)
+    if _profiler is not None:
+        def work(first, last):
+            """(flops, bytes) of entries first..last-1: two products per (query head, visible key) pair, the visible keys
+            and values read once."""
+            pairs = keys = toks = 0.0
+            for e in range(first, last):
+                n, s0 = ctx.q_start[e + 1] - ctx.q_start[e], ctx.start_pos[e]
+                full = n * s0 + n * (n + 1) / 2
+                pairs += min(full, n * window) if window else full
+                keys += min(s0 + n, window + n) if window else s0 + n
+                toks += n
+            return 2.0 * QH * (dk + dv) * pairs, (keys * KH * (dk + dv) + toks * QH * (dk + dv)) * q.element_size()
+        dec_work, pre_work = work(0, n_dec), work(n_dec, E)
+    if q.dtype != torch.bfloat16 or dk % 8 or dv % 8 or max(dk, dv) > 256:
+        # 32-bit, or head sizes the tensor-core kernels do not take: the plain kernel
+        paged_attention_ref(q, cache, group.block_table, ctx.tok_entry, ctx.positions, out, QH, KH, dk, group.page_size, window, scale,
+                            work=(dec_work[0] + pre_work[0], dec_work[1] + pre_work[1]), dv=dv, bias=bias)
+        return
+    gc = fa_group_chunk(QH // KH)
+    if n_dec:
+        # the keys a token sees (all before it, or its window) are split over CTAs while that fills the device
+        ctas = n_dec * KH * (QH // KH // gc)
+        keys = min(ctx.max_kv_len, window + 63) if window else ctx.max_kv_len
+        n_splits = max(1, min(DECODE_SLOTS // max(ctas, 1), -(-keys // 256), 16))
+        fa_decode(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, 0, n_dec, 0, n_splits, QH, KH, dk, group.page_size,
+                  window, scale, work=dec_work, dv=dv, bias=bias)
+    if E > n_dec and dk == 128 and dv == 128 and USE_TC_ATTENTION and USE_TMA_ATTENTION and tma_pages(group.page_size):
+        # heads of 128: the tcgen05 kernel
+        fa_prefill_tc(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, n_dec, E - n_dec,
+                      [ctx.q_start[e + 1] - ctx.q_start[e] for e in range(n_dec, E)], QH, KH, dk, group.page_size, window, scale,
+                      work=pre_work, bias=bias)
+    elif E > n_dec:
+        tpt = 64 // gc
+        n_tiles = sum(-(-(ctx.q_start[e + 1] - ctx.q_start[e]) // tpt) for e in range(n_dec, E))
+        fa_prefill(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, n_dec, E - n_dec, n_tiles, QH, KH, dk, group.page_size,
+                   window, scale, work=pre_work, dv=dv, bias=bias)
 
 
 RECURRENCE_FORMS = {"diagonal": 0, "delta_old_state": 1, "delta_gated_state": 2}
