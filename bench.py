@@ -84,7 +84,7 @@ DESIGN_SIZES = {"w2048": dict(width=2048, heads=16, ff=8192, layers=6), "w4096":
 
 
 def design_run(a, measure) -> int:
-    """--design silutar: the new design and the closest existing one (Qwen3) at equal layer sizes, bf16 random weights:
+    """--design silutar|damadra: that design and the closest existing one (Qwen3) at equal layer sizes, bf16 random weights:
     prefill of 2,048 tokens and decode at --batch requests of 2,048 tokens, device time by CUDA events, and one eager
     step of each kind by kernel family with each family's share of the measured peaks."""
     hbm_gbs, tf_burst, _, peak_src = measure.peaks(ROOT)
@@ -93,7 +93,8 @@ def design_run(a, measure) -> int:
     sizes = {}
     for name, sz in DESIGN_SIZES.items():
         row = {}
-        for design, make in (("silutar", measure.silutar_shape), ("qwen3", measure.qwen3_shape)):
+        for design, make in ((a.design, {"silutar": measure.silutar_shape, "damadra": measure.damadra_shape}[a.design]),
+                             ("qwen3", measure.qwen3_shape)):
             r = measure.time_design(make(**sz), prompt=2048, batch=a.batch, context=2048, steps=max(8, a.steps // 2),
                                     page_size=a.page_size, segments=not a.no_segments)
             for kind in ("decode", "prefill"):
@@ -106,7 +107,7 @@ def design_run(a, measure) -> int:
             row[design] = r
         sizes[name] = dict(sz, **row)
     clk = clocks.finish()
-    print(json.dumps({"metric": "prefill and decode tok/s of the Silutar design beside Qwen3 at equal layer sizes", "unit": "tokens/s",
+    print(json.dumps({"metric": f"prefill and decode tok/s of the {a.design.capitalize()} design beside Qwen3 at equal layer sizes", "unit": "tokens/s",
                       "n_gpus": 1, "dtype": "bf16", "data": "synthetic: random weights, uniform-random token ids",
                       "batch": a.batch, "prompt": 2048, "context": 2048, "families": "[us, launches, % of the measured peak]",
                       "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": tf_burst, "source": peak_src}, "sizes": sizes, "clocks": clk}))
@@ -126,7 +127,7 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page")
     ap.add_argument("--no-segments", action="store_true")
-    ap.add_argument("--design", default=None, choices=["silutar"],
+    ap.add_argument("--design", default=None, choices=["silutar", "damadra"],
                     help="instead of the default workload: prefill and decode of this design at a few layer sizes, beside "
                          "Qwen3 at equal sizes (random weights); prints one JSON line of its own")
     a = ap.parse_args()
@@ -141,7 +142,7 @@ def main() -> int:
     import torch
     from reinfer_b200 import measure, ops
 
-    if a.design == "silutar":
+    if a.design is not None:
         return design_run(a, measure)
 
     shape = a.shape.lower()

@@ -41,6 +41,10 @@ struct FtArgs {
     const void* next_w;                     // decode: a range to call into L2 once this CTA's tiles are requested
     long long next_bytes;
     int cluster_merge;                      // decode: the CTAs of one (request, kv head) are a cluster and merge themselves
+    // decode: a learned bias by distance, score += bias[min(i - j, bias_last)][h] (float [bias_last + 1, QH], in units of
+    // the scaled score; null: none); the last row stands for every greater distance
+    const float* bias;
+    int bias_last;
 };
 
 // With -DRB_TIMELINE a caller may hand the decode kernel a buffer of eight 64-bit words per CTA (linear block index) that
@@ -207,6 +211,8 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
 
     const int row0 = lane >> 2;
     const int pos0 = row0 < a.Gc ? pos : -1, pos1 = row0 + 8 < a.Gc ? pos : -1;
+    const float* bias0 = (a.bias && row0 < a.Gc) ? a.bias + head0 + row0 : nullptr;
+    const float* bias1 = (a.bias && row0 + 8 < a.Gc) ? a.bias + head0 + row0 + 8 : nullptr;
     float o[D / 8][4];
 #pragma unroll
     for (int j = 0; j < D / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f; }
@@ -313,6 +319,12 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
                 sc[j][1] = (key + 1 >= lo && key + 1 <= pos0) ? sc[j][1] * a.scale_log2 : -INFINITY;
                 sc[j][2] = (key >= lo && key <= pos1) ? sc[j][2] * a.scale_log2 : -INFINITY;
                 sc[j][3] = (key + 1 >= lo && key + 1 <= pos1) ? sc[j][3] * a.scale_log2 : -INFINITY;
+                if (a.bias) {                                  // (a masked place stays -inf whatever is added)
+                    constexpr float LOG2E = 1.4426950408889634f;
+                    const int d0 = min(max(pos - key, 0), a.bias_last), d1 = min(max(pos - key - 1, 0), a.bias_last);
+                    if (bias0) { sc[j][0] = fmaf(bias0[(size_t)d0 * a.QH], LOG2E, sc[j][0]); sc[j][1] = fmaf(bias0[(size_t)d1 * a.QH], LOG2E, sc[j][1]); }
+                    if (bias1) { sc[j][2] = fmaf(bias1[(size_t)d0 * a.QH], LOG2E, sc[j][2]); sc[j][3] = fmaf(bias1[(size_t)d1 * a.QH], LOG2E, sc[j][3]); }
+                }
                 mx0 = fmaxf(mx0, fmaxf(sc[j][0], sc[j][1]));
                 mx1 = fmaxf(mx1, fmaxf(sc[j][2], sc[j][3]));
             }
@@ -809,8 +821,10 @@ static int ft_launch(const CUtensorMap& map, const FtArgs& a, cudaStream_t s) {
 extern "C" int rb_fa_decode_tma(const void* q, const void* cache, long long num_pages, const int* block_table, const int* cu_q,
                                 const int* kv_len, void* out, float* part_o, float* part_lse, int first_entry, int n_entries,
                                 int first_tok, int n_splits, int QH, int KH, int d, int page_size, int max_pages, int window,
-                                float scale, const void* next_w, long long next_bytes, void* stream) {
+                                float scale, const void* next_w, long long next_bytes, const float* bias, int bias_rows,
+                                void* stream) {
     if (n_entries <= 0) return 0;
+    if (bias && bias_rows <= 0) RB_REFUSE("attention: a distance bias of %d rows", bias_rows);
     if ((uintptr_t)next_w & 15) RB_REFUSE("attention: the range to prefetch must start on a 16-byte boundary");
     if (QH <= 0 || KH <= 0 || QH % KH) RB_REFUSE("attention: %d query heads over %d kv heads", QH, KH);
     if (d <= 0 || d % 8 || d > 256) RB_REFUSE("attention (TMA): head_dim %d is not a multiple of 8 up to 256", d);
@@ -835,6 +849,7 @@ extern "C" int rb_fa_decode_tma(const void* q, const void* cache, long long num_
     a.scale_log2 = scale * 1.4426950408889634f;
     a.next_w = next_w; a.next_bytes = next_bytes;
     a.cluster_merge = cluster_merge ? 1 : 0;
+    a.bias = bias; a.bias_last = bias_rows - 1;
     CUtensorMap map;
     const int box_rows = page_size < FT_BN ? page_size : FT_BN;
     cudaStream_t s = (cudaStream_t)stream;

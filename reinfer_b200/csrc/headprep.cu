@@ -101,6 +101,68 @@ norm_heads_append_kernel(const TA* __restrict__ x, long long stride, const TW* _
     }
 }
 
+// The same for norms per head over heads of at most 256: a warp per (token, head), straight from global memory to
+// the destinations, no shared memory and no block-wide barrier.  Units of a token: its query heads, its key heads, and
+// (values of their own) its value heads.
+#define HPW_WARPS 8
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(HPW_WARPS * 32)
+norm_heads_append_warp_kernel(const TA* __restrict__ x, long long stride, const TW* __restrict__ qw, const TW* __restrict__ kw,
+                              const int* __restrict__ positions, const int* __restrict__ kv_slot, TA* __restrict__ q_out,
+                              TA* __restrict__ cache, int T, int QH, int KH, int d, int dv, int values_are_keys, int page_size,
+                              float eps, float temp_coef, int temp_every) {
+    pdl_trigger(); pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int per_tok = QH + (kv_slot ? KH + (values_are_keys ? 0 : KH) : 0);
+    const long long units = (long long)T * per_tok;
+    const size_t page_stride = (size_t)KH * page_size * (d + dv);
+    for (long long u = (long long)blockIdx.x * HPW_WARPS + (threadIdx.x >> 5); u < units; u += (long long)gridDim.x * HPW_WARPS) {
+        const int t = (int)(u / per_tok), idx = (int)(u % per_tok);
+        const TA* xr = x + (size_t)t * stride;
+        if (idx < QH) {
+            float v[8];
+            float ss = 0.0f;
+#pragma unroll
+            for (int m = 0; m < 8; ++m) { const int i = lane + 32 * m; v[m] = i < d ? to_f32(xr[idx * d + i]) : 0.0f; ss += v[m] * v[m]; }
+            ss = warp_sum(ss);
+            float f = 1.0f / sqrtf(ss / (float)d + eps);
+            if (temp_every > 0) f *= 1.0f + temp_coef * logf((float)((positions[t] + 1) / temp_every) + 1.0f);
+            TA* dst = q_out + ((size_t)t * QH + idx) * d;
+#pragma unroll
+            for (int m = 0; m < 8; ++m) { const int i = lane + 32 * m; if (i < d) dst[i] = from_f32<TA>(v[m] * f * to_f32(qw[i])); }
+            continue;
+        }
+        const int slot = kv_slot[t];
+        if (slot < 0) continue;                                // a padding row of a captured step stores nothing
+        const int page = slot / page_size, off = slot % page_size;
+        if (idx < QH + KH) {
+            const int hk = idx - QH;
+            const TA* src = xr + (size_t)QH * d + (size_t)hk * d;
+            float v[8];
+            float ss = 0.0f;
+#pragma unroll
+            for (int m = 0; m < 8; ++m) { const int i = lane + 32 * m; v[m] = i < d ? to_f32(src[i]) : 0.0f; ss += v[m] * v[m]; }
+            ss = warp_sum(ss);
+            const float f = 1.0f / sqrtf(ss / (float)d + eps);
+            TA* kdst = cache + (size_t)page * page_stride + ((size_t)hk * page_size + off) * d;
+            TA* vdst = cache + (size_t)page * page_stride + (size_t)KH * page_size * d + ((size_t)hk * page_size + off) * dv;
+#pragma unroll
+            for (int m = 0; m < 8; ++m) {
+                const int i = lane + 32 * m;
+                if (i < d) {
+                    kdst[i] = from_f32<TA>(v[m] * f * to_f32(kw[i]));
+                    if (values_are_keys) vdst[i] = from_f32<TA>(v[m]);
+                }
+            }
+        } else {
+            const int hv = idx - QH - KH;
+            const TA* src = xr + (size_t)(QH + KH) * d + (size_t)hv * dv;
+            TA* vdst = cache + (size_t)page * page_stride + (size_t)KH * page_size * d + ((size_t)hv * page_size + off) * dv;
+            for (int i = lane; i < dv; i += 32) vdst[i] = src[i];
+        }
+    }
+}
+
 extern "C" int rb_norm_heads_append(const void* x, long long stride, int dtype, const void* qw, const void* kw, int w_dtype,
                                     const int* positions, const int* kv_slot, void* q_out, void* cache,
                                     int T, int QH, int KH, int d, int dv, int q_group, int k_group, int values_are_keys,
@@ -113,9 +175,22 @@ extern "C" int rb_norm_heads_append(const void* x, long long stride, int dtype, 
     if (temp_every > 0 && !positions) RB_REFUSE("norm_heads_append: the queries' warm-up needs the positions");
     if (kv_slot && (!cache || page_size <= 0 || !kw)) RB_REFUSE("norm_heads_append: storing needs a cache, a page size and the keys' norm");
     if (!qw) RB_REFUSE("norm_heads_append: the queries' norm weight is missing");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (q_group == d && (!kv_slot || k_group == d) && d <= 256) {
+        // norms per head: a warp per (token, head)
+        const long long units = (long long)T * (QH + (kv_slot ? KH * (values_are_keys ? 1 : 2) : 0));
+        const int blocks = (int)((units + HPW_WARPS - 1) / HPW_WARPS < 148 * 8 ? (units + HPW_WARPS - 1) / HPW_WARPS : 148 * 8);
+#define RB_HPW(TA, TW) return rb_launch(norm_heads_append_warp_kernel<TA, TW>, dim3(blocks), dim3(HPW_WARPS * 32), 0, s, (const TA*)x, stride, \
+                                        (const TW*)qw, (const TW*)kw, positions, kv_slot, (TA*)q_out, (TA*)cache, T, QH, KH, d, dv, \
+                                        values_are_keys, page_size, eps, temp_coef, temp_every)
+        if (dtype == RB_F32 && w_dtype == RB_F32) RB_HPW(float, float);
+        if (dtype == RB_BF16 && w_dtype == RB_BF16) RB_HPW(bf16, bf16);
+        if (dtype == RB_BF16 && w_dtype == RB_F32) RB_HPW(bf16, float);
+#undef RB_HPW
+        RB_REFUSE("norm_heads_append: dtypes %d, %d", dtype, w_dtype);
+    }
     const size_t smem = (size_t)(QH + KH) * d * sizeof(float);
     if (smem > 200 * 1024) RB_REFUSE("norm_heads_append: %d floats of queries and keys per token", (QH + KH) * d);
-    cudaStream_t s = (cudaStream_t)stream;
 #define RB_HP(TA, TW) do { \
         if (smem > 48 * 1024) { \
             cudaError_t e = cudaFuncSetAttribute(norm_heads_append_kernel<TA, TW, TA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \

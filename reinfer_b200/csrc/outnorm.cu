@@ -9,20 +9,32 @@
 
 template <typename TW, int VEC>
 __global__ void residual_outnorm_kernel(float* __restrict__ x, const float* __restrict__ y, int n_parts, long long part_stride,
-                                        const TW* __restrict__ w, bf16* __restrict__ rounded, int h, float eps, float mult) {
+                                        const TW* __restrict__ w, bf16* __restrict__ rounded, int h, float eps, float mult,
+                                        const float* __restrict__ extra_a, const void* __restrict__ extra_src, int extra_bf16) {
     extern __shared__ __align__(16) float row[];
     __shared__ float red[32];
     pdl_trigger(); pdl_wait();
     const int r = blockIdx.x;
     const float* yr = y + (size_t)r * h;
+    // an optional multiple of another row joins y before the norm: y[r,:] += extra_a[r] * extra_src[r,:]
+    const float ea = extra_a ? extra_a[r] : 0.0f;
+    const float* ef = (extra_a && !extra_bf16) ? (const float*)extra_src + (size_t)r * h : nullptr;
+    const bf16* eb = (extra_a && extra_bf16) ? (const bf16*)extra_src + (size_t)r * h : nullptr;
     float ss = 0.0f;
     if (VEC == 4) {
         for (int i = threadIdx.x * 4; i < h; i += blockDim.x * 4) {
             float4 v = *reinterpret_cast<const float4*>(yr + i);
-            for (int s = 1; s < n_parts; ++s) {
-                const float4 d = *reinterpret_cast<const float4*>(yr + (size_t)s * part_stride + i);
-                v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+            for (int s0 = 1; s0 < n_parts; s0 += 8) {          // eight partial sums in flight, added in ascending order
+                float4 d[8];
+#pragma unroll
+                for (int p = 0; p < 8; ++p)
+                    d[p] = s0 + p < n_parts ? *reinterpret_cast<const float4*>(yr + (size_t)(s0 + p) * part_stride + i)
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int p = 0; p < 8; ++p) if (s0 + p < n_parts) { v.x += d[p].x; v.y += d[p].y; v.z += d[p].z; v.w += d[p].w; }
             }
+            if (ef) { v.x = fmaf(ea, ef[i], v.x); v.y = fmaf(ea, ef[i + 1], v.y); v.z = fmaf(ea, ef[i + 2], v.z); v.w = fmaf(ea, ef[i + 3], v.w); }
+            if (eb) { v.x = fmaf(ea, to_f32(eb[i]), v.x); v.y = fmaf(ea, to_f32(eb[i + 1]), v.y); v.z = fmaf(ea, to_f32(eb[i + 2]), v.z); v.w = fmaf(ea, to_f32(eb[i + 3]), v.w); }
             *reinterpret_cast<float4*>(row + i) = v;
             ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
         }
@@ -30,6 +42,8 @@ __global__ void residual_outnorm_kernel(float* __restrict__ x, const float* __re
         for (int i = threadIdx.x; i < h; i += blockDim.x) {
             float v = yr[i];
             for (int s = 1; s < n_parts; ++s) v += yr[(size_t)s * part_stride + i];
+            if (ef) v = fmaf(ea, ef[i], v);
+            if (eb) v = fmaf(ea, to_f32(eb[i]), v);
             row[i] = v;
             ss += v * v;
         }
@@ -62,22 +76,29 @@ __global__ void residual_outnorm_kernel(float* __restrict__ x, const float* __re
 }
 
 // y: n_parts stacked [rows, h] float arrays, part_stride elements apart.  rounded: bfloat16 [rows, h] or null.
+// extra_a [rows] float with extra_src [rows, h] (float or bfloat16), or neither.
 extern "C" int rb_residual_outnorm(float* x, const float* y, int n_parts, long long part_stride, const void* w, int w_dtype,
-                                   void* rounded, int rows, int h, float eps, float mult, void* stream) {
+                                   void* rounded, int rows, int h, float eps, float mult, const float* extra_a,
+                                   const void* extra_src, int extra_dtype, void* stream) {
     if (rows <= 0) return 0;
+    if ((extra_a == nullptr) != (extra_src == nullptr)) RB_REFUSE("outnorm: half an extra term");
     if (h <= 0 || n_parts < 1) RB_REFUSE("outnorm: width %d, %d partial sums", h, n_parts);
     const size_t smem = (size_t)h * sizeof(float);
     if (smem > 200 * 1024) RB_REFUSE("outnorm: a row of %d floats does not fit shared memory", h);
     cudaStream_t s = (cudaStream_t)stream;
     const bool vec = h % 4 == 0 && part_stride % 4 == 0 && ((uintptr_t)x | (uintptr_t)y) % 16 == 0 && (!rounded || (uintptr_t)rounded % 8 == 0);
-    const int threads = h >= 4096 ? 512 : (h >= 1024 ? 256 : 128);
+    // a stack of partial sums over few rows: a thread per 16 bytes of the row, so that all of a row's loads are in flight
+    // at once (the order of the sums is then a function of the width and of whether the input is a stack - never of
+    // the other rows)
+    int threads = h >= 4096 ? 512 : (h >= 1024 ? 256 : 128);
+    if (vec && n_parts > 1) { threads = ((h / 4 + 31) / 32) * 32; if (threads > 1024) threads = 1024; if (threads < 128) threads = 128; }
 #define RB_ON(TW, V) do { \
         if (smem > 48 * 1024) { \
             cudaError_t e = cudaFuncSetAttribute(residual_outnorm_kernel<TW, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) return (int)e; \
         } \
         return rb_launch(residual_outnorm_kernel<TW, V>, dim3(rows), dim3(threads), smem, s, x, y, n_parts, part_stride, \
-                         (const TW*)w, (bf16*)rounded, h, eps, mult); } while (0)
+                         (const TW*)w, (bf16*)rounded, h, eps, mult, extra_a, extra_src, extra_dtype == RB_BF16 ? 1 : 0); } while (0)
     if (w_dtype == RB_F32) { if (vec) RB_ON(float, 4); else RB_ON(float, 1); }
     if (w_dtype == RB_BF16) { if (vec) RB_ON(bf16, 4); else RB_ON(bf16, 1); }
 #undef RB_ON

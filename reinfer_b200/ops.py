@@ -460,8 +460,10 @@ def decode_cluster_slots(d: int, n: int) -> int:
 
 
 def fa_decode_tma(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, first_tok: int, n_splits: int,
-                  QH: int, KH: int, d: int, page_size: int, window: int, scale: float, work=(0.0, 0.0)) -> None:
-    """Split-K flash decoding with the key/value tiles brought in by TMA (page size a power of two >= 8).
+                  QH: int, KH: int, d: int, page_size: int, window: int, scale: float, work=(0.0, 0.0),
+                  bias: Optional[torch.Tensor] = None) -> None:
+    """Split-K flash decoding with the key/value tiles brought in by TMA (page size a power of two >= 8); bias as in
+    paged_attention_ref.
     Up to 16 splits whose CTAs are all resident at once form clusters that merge their results themselves (no scratch,
     no merge kernel); several waves of CTAs, or more splits, go through scratch and the merge kernel (clusters
     that wait for a free place on one GPC were measured slower there)."""
@@ -475,7 +477,8 @@ def fa_decode_tma(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_
     _check(lib().rb_fa_decode_tma(_p(q), _p(cache), c_longlong(cache.shape[0]), _p(block_table), _p(cu_q), _p(kv_len), _p(out),
                                   _p(part_o), _p(part_lse), c_int(first_entry), c_int(n_entries), c_int(first_tok),
                                   c_int(n_splits), c_int(QH), c_int(KH), c_int(d), c_int(page_size),
-                                  c_int(block_table.shape[1]), c_int(window), c_float(scale), nw, nb, _stream()), "fa_decode_tma", *work)
+                                  c_int(block_table.shape[1]), c_int(window), c_float(scale), nw, nb, *_bias_args(bias, QH), _stream()),
+           "fa_decode_tma", *work)
 
 
 def fa_prefill_tma(q, cache, block_table, cu_q, kv_len, out, first_entry: int, n_entries: int, n_tiles: int,
@@ -1005,10 +1008,10 @@ def chunk_attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch
 
 
 def residual_outnorm(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float, mult: float,
-                     rounded: Optional[torch.Tensor] = None) -> None:
+                     rounded: Optional[torch.Tensor] = None, extra=None) -> None:
     """x (float32 [rows, h]) += mult * rms(y) * w with y float32 [rows, h] or a stack [S, rows, h] of partial sums
     (added in ascending order) and rms(y) = y / sqrt(mean(y^2) + eps); `rounded` (bfloat16 [rows, h]) receives
-    the new x once more, rounded."""
+    the new x once more, rounded.  extra = (a float32 [rows], src [rows, h]): y[r,:] gets a[r] * src[r,:] added first."""
     _need(x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2, "outnorm: x float32 [rows, h] contiguous")
     rows, h = x.shape
     _need(y.dtype == torch.float32 and y.is_contiguous() and y.shape[-1] == h and y.numel() % max(x.numel(), 1) == 0 and y.numel() >= x.numel(),
@@ -1017,8 +1020,14 @@ def residual_outnorm(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: flo
           "outnorm: the rounded copy is bfloat16 of x's shape")
     if rows == 0:
         return
+    ea = es = None
+    if extra is not None:
+        ea, es = extra
+        _need(ea.dtype == torch.float32 and ea.numel() == rows and es.is_contiguous() and tuple(es.shape) == (rows, h),
+              "outnorm: the extra term is a float32 factor per row and rows of x's shape")
     _check(lib().rb_residual_outnorm(_p(x), _p(y), c_int(y.numel() // x.numel()), c_longlong(x.numel()), _p(w), c_int(dt(w)),
-                                     _p(rounded), c_int(rows), c_int(h), c_float(eps), c_float(mult), _stream()),
+                                     _p(rounded), c_int(rows), c_int(h), c_float(eps), c_float(mult), _p(ea), _p(es),
+                                     c_int(dt(es) if es is not None else F32), _stream()),
            "residual_outnorm", 0.0, float((y.numel() + 2 * x.numel()) * 4 + (2 * x.numel() if rounded is not None else 0)))
 
 
@@ -1062,6 +1071,21 @@ def moe_route(z: torch.Tensor, corr: Optional[torch.Tensor], experts: int, top: 
     ident = torch.empty((T,), dtype=torch.float32, device=z.device) if n > experts else None
     _check(lib().rb_moe_route(_p(z), _p(corr), _p(gates), _p(ident), c_int(T), c_int(n), c_int(experts), c_int(top), _stream()),
            "moe_route")
+    return gates, ident
+
+
+def moe_router(x: torch.Tensor, w: torch.Tensor, corr: Optional[torch.Tensor], experts: int, top: int):
+    """The router's product z = x w^T (32-bit, one fixed order per output) and moe_route's choice in one kernel:
+    x [T, h], w [n, h] -> (gates float32 [T, experts], ident float32 [T] or None)."""
+    _need(x.is_contiguous() and w.is_contiguous() and x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1],
+          "moe_router: x [T, h], w [n, h] contiguous")
+    T, n = x.shape[0], w.shape[0]
+    _need(corr is None or (corr.dtype == torch.float32 and corr.numel() == n), "moe_router: the correction is float32 [n]")
+    gates = torch.empty((T, experts), dtype=torch.float32, device=x.device)
+    ident = torch.empty((T,), dtype=torch.float32, device=x.device) if n > experts else None
+    _check(lib().rb_moe_router(_p(x), c_int(dt(x)), _p(w), c_int(dt(w)), _p(corr), _p(gates), _p(ident), c_int(T), c_int(x.shape[1]),
+                               c_int(n), c_int(experts), c_int(top), _stream()), "moe_router",
+           2.0 * T * n * x.shape[1], float(x.numel() * x.element_size() + w.numel() * w.element_size()))
     return gates, ident
 
 
@@ -1115,8 +1139,13 @@ def biased_attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torc
         ctas = n_dec * KH * (QH // KH // gc)
         keys = min(ctx.max_kv_len, window + 63) if window else ctx.max_kv_len
         n_splits = max(1, min(DECODE_SLOTS // max(ctas, 1), -(-keys // 256), 16))
-        fa_decode(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, 0, n_dec, 0, n_splits, QH, KH, dk, group.page_size,
-                  window, scale, work=dec_work, dv=dv, bias=bias)
+        if dk == dv and tma_pages(group.page_size) and USE_TMA_ATTENTION:
+            # key size = value size: the kernel whose tiles come by TMA (up to 16 splits merge inside their cluster)
+            fa_decode_tma(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, 0, n_dec, 0, n_splits, QH, KH, dk, group.page_size,
+                          window, scale, work=dec_work, bias=bias)
+        else:
+            fa_decode(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, 0, n_dec, 0, n_splits, QH, KH, dk, group.page_size,
+                      window, scale, work=dec_work, dv=dv, bias=bias)
     if E > n_dec and dk == 128 and dv == 128 and USE_TC_ATTENTION and USE_TMA_ATTENTION and tma_pages(group.page_size):
         # heads of 128: the tcgen05 kernel
         fa_prefill_tc(q, cache, group.block_table, ctx.cu_q, ctx.kv_len, out, n_dec, E - n_dec,

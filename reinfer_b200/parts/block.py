@@ -133,14 +133,17 @@ class OutNormBlock:
         h = self._reads(ctx, x)
         y = torch.empty(x.shape, dtype=torch.float32, device=x.device)
         ctx.fresh_residual, ctx.norm_ahead = True, None
+        ctx.takes_row_multiple, ctx.row_multiple = True, None
         try:
             left = run(h, y)
             if left is None and ctx.fresh_residual and x.shape[0]:
                 raise RuntimeError("block 'out_norm': the sublayer did not hand over its output (parts.linear.matmul_into_residual)")
+            extra = ctx.row_multiple
         finally:
-            ctx.fresh_residual = False
+            ctx.fresh_residual = ctx.takes_row_multiple = False
+            ctx.row_multiple = None
         rounded = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device) if ctx.dtype == torch.bfloat16 else None
-        norm.add(ctx, x, y if left is None else left, rounded)
+        norm.add(ctx, x, y if left is None else left, rounded, extra=extra)
         ctx.rounded_stream = rounded
 
     def forward(self, ctx, x, cache, delta=None):

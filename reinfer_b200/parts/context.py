@@ -69,6 +69,10 @@ class StepContext:
     # The tensor a part was handed as `residual` holds nothing yet: the first product into it stores instead of
     # adding and clears this (`matmul_into_residual`).  Set by a block that wants a sublayer's output by itself.
     fresh_residual: bool = False
+    # A block that can add a per-row multiple of other rows to a sublayer's output says so (`takes_row_multiple`); a part
+    # may then leave (factors float32 [T], rows [T, h]) in `row_multiple` instead of adding them itself.
+    takes_row_multiple: bool = False
+    row_multiple: Optional[tuple] = None
 
     def empty(self, shape, dtype=None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)

@@ -53,16 +53,18 @@ class ExpertMixture(FeedForward):
 
     def forward(self, ctx, xn, residual):
         T = xn.shape[0]
-        z = torch.empty((T, self.E + self.I), dtype=torch.float32, device=xn.device)
-        ops.gemm_ref(xn, self.w_router, z)                               # the router in 32-bit, one chain per output
-        gates, ident = ops.moe_route(z, self.correction, self.E, self.top)
+        gates, ident = ops.moe_router(xn, self.w_router, self.correction, self.E, self.top)     # 32-bit, product and choice
         act = ops.relu2_gate(matmul(ctx, xn, self.w_up), gates, self.ff)
         if ident is not None:
             ctx.norm_ahead = None           # the stream is not complete behind the down product: nobody's rows can be made there
         left = matmul_into_residual(ctx, act, self.w_down, residual)
         if ident is not None and T:
-            # the identity experts' share: the token's own row times the sum of their chosen scores
-            ops.rows_axpy(residual if left is None else left[0], ident, xn)
+            # the identity experts' share: the token's own row times the sum of their chosen scores - left to the
+            # block where it adds such a term on its way, else added here
+            if getattr(ctx, "takes_row_multiple", False) and getattr(ctx, "row_multiple", None) is None:
+                ctx.row_multiple = (ident, xn)
+            else:
+                ops.rows_axpy(residual if left is None else left[0], ident, xn)
         return left
 
 

@@ -70,8 +70,9 @@ class ResidualOutNorm(Norm):
     def bind(self, tensors):
         self.weight = tensors[self.weight_name]
 
-    def add(self, ctx, x, y, rounded=None) -> None:
-        ops.residual_outnorm(x, y, self.weight, self.eps, self.mult, rounded=rounded)
+    def add(self, ctx, x, y, rounded=None, extra=None) -> None:
+        """extra = (a [rows], src [rows, width]): a[r] * src[r] joins y[r] before the norm."""
+        ops.residual_outnorm(x, y, self.weight, self.eps, self.mult, rounded=rounded, extra=extra)
 
     def forward(self, ctx, x, out=None, delta=None, row_idx=None):
         raise TypeError("an output norm has no rows to hand on: the block calls add(ctx, x, y)")

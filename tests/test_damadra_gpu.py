@@ -173,7 +173,7 @@ def test_a_small_real_shape_on_the_tensor_core_paths(tmp_path, dtype):
         ops.set_profiler(old)
     names = set(prof.summary())
     if dtype == "bfloat16":
-        assert {"fa_prefill_tc", "fa_prefill", "fa_decode", "residual_outnorm", "moe_route"} <= names, names
+        assert {"fa_prefill_tc", "fa_prefill", "fa_decode_tma", "residual_outnorm", "moe_router"} <= names, names
         assert "paged_attention_ref" not in names, names
     else:
         assert "paged_attention_ref" in names and any(n.startswith("gemm_fma") for n in names), names

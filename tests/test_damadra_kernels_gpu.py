@@ -53,6 +53,14 @@ def test_output_norm_adds_to_the_stream(h, parts, wdtype):
     ops.residual_outnorm(xd, y.to(DEV) if parts > 1 else y[0].to(DEV), w.to(DEV), eps, mult, rounded=rounded)
     assert (xd.cpu().double() - ref).abs().max() < 2e-5
     assert torch.equal(rounded.cpu(), xd.cpu().to(torch.bfloat16))
+    # with a multiple of other rows joining y before the norm
+    a = torch.rand(rows, generator=g)
+    for sdt in (torch.float32, torch.bfloat16):
+        src = torch.randn(rows, h, generator=g).to(sdt)
+        ref2 = x.double() + mult * plain.rms(y.double().sum(0) + a.double()[:, None] * src.double(), eps) * w.double()
+        x2 = x.to(DEV)
+        ops.residual_outnorm(x2, y.to(DEV) if parts > 1 else y[0].to(DEV), w.to(DEV), eps, mult, extra=(a.to(DEV), src.to(DEV)))
+        assert (x2.cpu().double() - ref2).abs().max() < 2e-5
     # a row's result does not depend on the rows beside it
     x1 = x[2:3].to(DEV).contiguous()
     ops.residual_outnorm(x1, y[:, 2:3].contiguous().to(DEV) if parts > 1 else y[0, 2:3].contiguous().to(DEV), w.to(DEV), eps, mult)
@@ -302,10 +310,35 @@ def test_router_choice_and_weights(n, E, top):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_gated_squared_relu_and_identity_share(dtype):
+@pytest.mark.parametrize("h,n,E,top", [(52, 3, 3, 1), (64, 7, 5, 3), (96, 4, 2, 4), (256, 12, 8, 4), (1000, 37, 30, 5)])
+def test_router_product_and_choice_in_one(dtype, h, n, E, top):
+    """The fused router against the plain route(): the same experts, the same weights; and a token's row alone gives
+    the same bits as in the batch."""
+    from reinfer_b200 import ops
+    g = _gen(h + n)
+    T = 40
+    x = torch.randn(T, h, generator=g).to(dtype)
+    w = (torch.randn(n, h, generator=g) * 3 / h ** 0.5).to(dtype)
+    corr = torch.randn(n, generator=g) * 0.2
+    gates, ident = ops.moe_router(x.to(DEV), w.to(DEV), corr.to(DEV), E, top)
+    W = {"p.router": w.double(), "p.correction": corr.double()}
+    chosen, weight = plain.route(x.double(), W, "p.", {"top": top})
+    ref = torch.zeros(T, n, dtype=torch.float64)
+    ref.scatter_(1, chosen, weight)
+    assert (gates.double().cpu() - ref[:, :E]).abs().max() < 2e-6
+    assert ((gates.cpu() != 0) == (ref[:, :E] != 0)).all()
+    if n > E:
+        assert (ident.double().cpu() - ref[:, E:].sum(1)).abs().max() < 2e-6
+    g1, i1 = ops.moe_router(x[17:18].contiguous().to(DEV), w.to(DEV), corr.to(DEV), E, top)
+    assert torch.equal(g1[0], gates[17]) and (ident is None or torch.equal(i1[0], ident[17]))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("ff", [10, 16])
+def test_gated_squared_relu_and_identity_share(dtype, ff):
     from reinfer_b200 import ops
     g = _gen(5)
-    T, E, ff, h = 6, 3, 10, 20
+    T, E, h = 6, 3, 20
     u = (torch.randn(T, E * ff, generator=g) * 2).to(dtype)
     gates = torch.rand(T, E, generator=g)
     gates[gates < 0.4] = 0.0
