@@ -72,8 +72,9 @@ class ClockSampler(threading.Thread):
                 if v.lower().startswith("active"):
                     reasons.add(n)
         sm.sort()
+        # (sm_mhz_top: the highest sample - a run of short timed regions between host-side set-up idles in most samples)
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "sm_mhz_top": sm[-1] if sm else None}
 
 
 REFERENCE_UNAVAILABLE = ("the reference is a Rust workspace (no Python package, no cargo/rustc in this image): "
