@@ -21,8 +21,8 @@
 // sees only the keys from the start of its own chunk of `chunk` positions, counted from position 0) and a penalty on
 // distance per query head, score -= r1[h] ln(1 + r2[h] (i - j)), added in the exponent's base-2 domain as
 // r1 log2(1 + r2 (i - j)); and a factor on the output.  Two more serve attention with a learned bias by distance and
-// value heads of their own size: a float table bias[min(i - j, rows - 1)][head] that is added to the scaled score
-// (the last row stands for every greater distance), and dv != d (a page is then [K: KH x page x d | V: KH x page x
+// value heads of their own size: a float table bias[head][min(i - j, rows - 1)] that is added to the scaled score
+// (the last column stands for every greater distance), and dv != d (a page is then [K: KH x page x d | V: KH x page x
 // dv]; the tiles are as wide as the larger of the two, the narrower zero-filled).  Without them the kernels are
 // what they were.
 //
@@ -55,7 +55,7 @@ struct FaArgs {
     const float* r2;
     float out_scale;
     int dv;                            // the value heads' size (= d unless the layer says otherwise)
-    const float* bias;                 // [bias_rows, QH] added to the scaled scores by distance (null: none)
+    const float* bias;                 // [QH, bias_rows] added to the scaled scores by distance (null: none)
     int bias_rows;
 };
 
@@ -278,8 +278,8 @@ fa_prefill_kernel(const FaArgs a) {
     const bool pen = a.r1 != nullptr;
     const int hd0 = head0 + r0 % a.Gc, hd1 = head0 + r1 % a.Gc;
     const float pa0 = pen ? a.r1[hd0] : 0.0f, pb0 = pen ? a.r2[hd0] : 0.0f, pa1 = pen ? a.r1[hd1] : 0.0f, pb1 = pen ? a.r2[hd1] : 0.0f;
-    const float* bias0 = a.bias ? a.bias + hd0 : nullptr;
-    const float* bias1 = a.bias ? a.bias + hd1 : nullptr;
+    const float* bias0 = a.bias ? a.bias + (size_t)hd0 * a.bias_rows : nullptr;
+    const float* bias1 = a.bias ? a.bias + (size_t)hd1 * a.bias_rows : nullptr;
     // keys beyond the last row of this WARP are masked for all its rows: the warp may stop early
     const int warp_last_tok = min(n_tok - 1, (warp * 16 + 15) / a.Gc);
     const int warp_t_end = (warp * 16) / a.Gc < n_tok ? (start_pos + q0 + warp_last_tok) / FA_BN + 1 : 0;
@@ -301,7 +301,7 @@ fa_prefill_kernel(const FaArgs a) {
             const unsigned char* sK = stages + buf * FaSmem<D>::STAGE;
             fa_tile<D, FA_BN / 8>(sQ + warp * 16 * FaSmem<D>::STRIDE, sK, sK + FaSmem<D>::TILE, 0, t * FA_BN,
                                   pos0, pos1, lo0, lo1, a.scale_log2, o, m, l, pen, pa0, pb0, pa1, pb1,
-                                  bias0, bias1, a.QH, a.bias_rows - 1);
+                                  bias0, bias1, 1, a.bias_rows - 1);
         }
     }
     cp_async_wait<0>();
@@ -353,8 +353,8 @@ fa_decode_kernel(const FaArgs a) {
     const bool pen = a.r1 != nullptr;
     const float pa0 = (pen && row0 < a.Gc) ? a.r1[head0 + row0] : 0.0f, pb0 = (pen && row0 < a.Gc) ? a.r2[head0 + row0] : 0.0f;
     const float pa1 = (pen && row0 + 8 < a.Gc) ? a.r1[head0 + row0 + 8] : 0.0f, pb1 = (pen && row0 + 8 < a.Gc) ? a.r2[head0 + row0 + 8] : 0.0f;
-    const float* bias0 = (a.bias && row0 < a.Gc) ? a.bias + head0 + row0 : nullptr;
-    const float* bias1 = (a.bias && row0 + 8 < a.Gc) ? a.bias + head0 + row0 + 8 : nullptr;
+    const float* bias0 = (a.bias && row0 < a.Gc) ? a.bias + (size_t)(head0 + row0) * a.bias_rows : nullptr;
+    const float* bias1 = (a.bias && row0 + 8 < a.Gc) ? a.bias + (size_t)(head0 + row0 + 8) * a.bias_rows : nullptr;
     float o[D / 8][4];
 #pragma unroll
     for (int j = 0; j < D / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f; }
@@ -374,7 +374,7 @@ fa_decode_kernel(const FaArgs a) {
         cp_async_commit();
         const unsigned char* sK = stages + (it % NST) * FaSmem<D>::STAGE;
         fa_tile<D, 2>(sQ, sK, sK + FaSmem<D>::TILE, warp * 16, t * FA_BN, pos0, pos1, lo, lo, a.scale_log2, o, m, l, pen, pa0, pb0, pa1, pb1,
-                      bias0, bias1, a.QH, a.bias_rows - 1);
+                      bias0, bias1, 1, a.bias_rows - 1);
     }
     cp_async_wait<0>();
     __syncthreads();                                           // the stages are free: reuse them for the merge

@@ -8,8 +8,8 @@
 // the faster bfloat16 kernels.
 // Beyond the plain form it takes: a value head size of its own (dv != d), a chunk mask (a token sees the
 // keys of its own chunk of `chunk` positions, counted from position 0), a logarithmic distance penalty per
-// query head (score -= r1[h] * ln(1 + r2[h] * (i - j))), a learned bias by distance (score += bias[min(i - j,
-// rows - 1)][h], a float table [rows, QH] whose last row stands for every greater distance), and a factor on the output.
+// query head (score -= r1[h] * ln(1 + r2[h] * (i - j))), a learned bias by distance (score += bias[h][min(i - j,
+// rows - 1)], a float table [QH, rows] whose last column stands for every greater distance), and a factor on the output.
 // (reference semantics: crates/cuda/kernels/decode_gqa_kernels.cu:99-136 page lookup
 //  page[t/block_len]; decode_flash_kernels.cu:212-349 max/exp/sum/PV in f32.)
 #include "common.cuh"
@@ -72,7 +72,7 @@ paged_attention_ref_kernel(const TA* __restrict__ q, const TC* __restrict__ cach
             for (int i = 0; i < d; ++i) dot = fmaf(qs[i], to_f32(krow[i]), dot);
             s = dot * scale;
             if (r1) s -= pen1 * log1pf(pen2 * (float)(pos - key));
-            if (bias) s += bias[(size_t)min(pos - key, bias_rows - 1) * QH + hq];
+            if (bias) s += bias[(size_t)hq * bias_rows + min(pos - key, bias_rows - 1)];
         }
         const float bm = warp_max(s);
         if (bm == -INFINITY) continue;                         // no key in this block (warp-uniform)
@@ -105,7 +105,7 @@ paged_attention_ref_kernel(const TA* __restrict__ q, const TC* __restrict__ cach
 }
 
 // dv: the value heads' size (0: as d).  chunk 0: no chunk mask.  r1, r2 [QH] float: the distance penalty (null: none).
-// bias [bias_rows, QH] float: the bias by distance (null: none).
+// bias [QH, bias_rows] float: the bias by distance (null: none).
 extern "C" int rb_paged_attention_ref(const void* q, const void* cache, int dtype,
                                       const int* block_table, const int* tok_row, const int* positions,
                                       void* out, int n_tokens, int QH, int KH, int d, int page_size,

@@ -77,8 +77,8 @@ struct FcArgs {
     const float* r1;
     const float* r2;
     float out_scale;
-    // A learned bias by distance: score += bias[min(i - j, bias_last)][h] (a float table [bias_last + 1, QH] in units of
-    // the scaled score; null: none).  Its last row stands for every greater distance.
+    // A learned bias by distance: score += bias[h][min(i - j, bias_last)] (a float table [QH, bias_last + 1] in units of
+    // the scaled score; null: none).  Its last column stands for every greater distance.
     const float* bias;
     int bias_last;
 };
@@ -396,9 +396,9 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
         const float pen_a = pen ? a.r1[head0 + row % a.Gc] / a.scale_log2 : 0.0f, pen_b = pen ? a.r2[head0 + row % a.Gc] : 0.0f;
         // the bias by distance of this row's head, in units of the raw score like the penalty; a tile whose keys all lie
         // at least bias_last behind the row gets one constant
-        const float* brow = a.bias ? a.bias + head0 + row % a.Gc : nullptr;
+        const float* brow = a.bias ? a.bias + (size_t)(head0 + row % a.Gc) * (a.bias_last + 1) : nullptr;
         const float bias_unit = 1.4426950408889634f / a.scale_log2;
-        const float bias_far = brow ? brow[(size_t)a.bias_last * a.QH] * bias_unit : 0.0f;
+        const float bias_far = brow ? brow[a.bias_last] * bias_unit : 0.0f;
         // m: the maximum that P and O are scaled to (it follows the true maximum only in steps larger than
         // FC_RESCALE, so that O can stay in tensor memory and be accumulated by the MMA itself); l: the sum in that scale
         float m = -INFINITY, l = 0.0f;
@@ -454,7 +454,7 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
 #pragma unroll
                     for (int j = 0; j < FC_BN; ++j) {
                         const int dist = min(max(d0 - j, 0), a.bias_last);
-                        sr[j] = __float_as_uint(fmaf(brow[(size_t)dist * a.QH], bias_unit, __uint_as_float(sr[j])));
+                        sr[j] = __float_as_uint(fmaf(brow[dist], bias_unit, __uint_as_float(sr[j])));
                     }
                 }
             }

@@ -41,8 +41,8 @@ struct FtArgs {
     const void* next_w;                     // decode: a range to call into L2 once this CTA's tiles are requested
     long long next_bytes;
     int cluster_merge;                      // decode: the CTAs of one (request, kv head) are a cluster and merge themselves
-    // decode: a learned bias by distance, score += bias[min(i - j, bias_last)][h] (float [bias_last + 1, QH], in units of
-    // the scaled score; null: none); the last row stands for every greater distance
+    // decode: a learned bias by distance, score += bias[h][min(i - j, bias_last)] (float [QH, bias_last + 1], in units of
+    // the scaled score; null: none); the last column stands for every greater distance
     const float* bias;
     int bias_last;
 };
@@ -211,8 +211,8 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
 
     const int row0 = lane >> 2;
     const int pos0 = row0 < a.Gc ? pos : -1, pos1 = row0 + 8 < a.Gc ? pos : -1;
-    const float* bias0 = (a.bias && row0 < a.Gc) ? a.bias + head0 + row0 : nullptr;
-    const float* bias1 = (a.bias && row0 + 8 < a.Gc) ? a.bias + head0 + row0 + 8 : nullptr;
+    const float* bias0 = (a.bias && row0 < a.Gc) ? a.bias + (size_t)(head0 + row0) * (a.bias_last + 1) : nullptr;
+    const float* bias1 = (a.bias && row0 + 8 < a.Gc) ? a.bias + (size_t)(head0 + row0 + 8) * (a.bias_last + 1) : nullptr;
     float o[D / 8][4];
 #pragma unroll
     for (int j = 0; j < D / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f; }
@@ -322,8 +322,8 @@ fa_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const FtArgs a)
                 if (a.bias) {                                  // (a masked place stays -inf whatever is added)
                     constexpr float LOG2E = 1.4426950408889634f;
                     const int d0 = min(max(pos - key, 0), a.bias_last), d1 = min(max(pos - key - 1, 0), a.bias_last);
-                    if (bias0) { sc[j][0] = fmaf(bias0[(size_t)d0 * a.QH], LOG2E, sc[j][0]); sc[j][1] = fmaf(bias0[(size_t)d1 * a.QH], LOG2E, sc[j][1]); }
-                    if (bias1) { sc[j][2] = fmaf(bias1[(size_t)d0 * a.QH], LOG2E, sc[j][2]); sc[j][3] = fmaf(bias1[(size_t)d1 * a.QH], LOG2E, sc[j][3]); }
+                    if (bias0) { sc[j][0] = fmaf(bias0[d0], LOG2E, sc[j][0]); sc[j][1] = fmaf(bias0[d1], LOG2E, sc[j][1]); }
+                    if (bias1) { sc[j][2] = fmaf(bias1[d0], LOG2E, sc[j][2]); sc[j][3] = fmaf(bias1[d1], LOG2E, sc[j][3]); }
                 }
                 mx0 = fmaxf(mx0, fmaxf(sc[j][0], sc[j][1]));
                 mx1 = fmaxf(mx1, fmaxf(sc[j][2], sc[j][3]));

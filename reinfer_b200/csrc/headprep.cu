@@ -105,7 +105,43 @@ norm_heads_append_kernel(const TA* __restrict__ x, long long stride, const TW* _
 // the destinations, no shared memory and no block-wide barrier.  Units of a token: its query heads, its key heads, and
 // (values of their own) its value heads.
 #define HPW_WARPS 8
-template <typename TA, typename TW>
+// V consecutive elements of a row as floats (V = 4: one 8-byte or 16-byte access; V = 1: one element)
+template <int V> __device__ __forceinline__ void hp_load(const bf16* p, float (&v)[V]) {
+    if (V == 4) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        const float2 a = __bfloat1622float2(h2[0]), b = __bfloat1622float2(h2[1]);
+        v[0] = a.x; v[1] = a.y; v[V > 2 ? 2 : 0] = b.x; v[V > 3 ? 3 : 0] = b.y;
+    } else {
+        v[0] = __bfloat162float(p[0]);
+    }
+}
+template <int V> __device__ __forceinline__ void hp_load(const float* p, float (&v)[V]) {
+    if (V == 4) {
+        const float4 a = *reinterpret_cast<const float4*>(p);
+        v[0] = a.x; v[1] = a.y; v[V > 2 ? 2 : 0] = a.z; v[V > 3 ? 3 : 0] = a.w;
+    } else {
+        v[0] = p[0];
+    }
+}
+template <int V> __device__ __forceinline__ void hp_store(bf16* p, const float (&v)[V]) {
+    if (V == 4) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[V > 2 ? 2 : 0], v[V > 3 ? 3 : 0]);
+        uint2 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&lo); pk.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p) = pk;
+    } else {
+        p[0] = __float2bfloat16_rn(v[0]);
+    }
+}
+template <int V> __device__ __forceinline__ void hp_store(float* p, const float (&v)[V]) {
+    if (V == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[V > 2 ? 2 : 0], v[V > 3 ? 3 : 0]);
+    else p[0] = v[0];
+}
+
+// V: elements a lane takes at a time (4 where the head sizes are multiples of 4 and everything is aligned, else 1);
+// M: passes of 32 * V elements that cover a head of at most 256.
+template <typename TA, typename TW, int V, int M>
 __global__ void __launch_bounds__(HPW_WARPS * 32)
 norm_heads_append_warp_kernel(const TA* __restrict__ x, long long stride, const TW* __restrict__ qw, const TW* __restrict__ kw,
                               const int* __restrict__ positions, const int* __restrict__ kv_slot, TA* __restrict__ q_out,
@@ -114,51 +150,54 @@ norm_heads_append_warp_kernel(const TA* __restrict__ x, long long stride, const 
     pdl_trigger(); pdl_wait();
     const int lane = threadIdx.x & 31;
     const int per_tok = QH + (kv_slot ? KH + (values_are_keys ? 0 : KH) : 0);
-    const long long units = (long long)T * per_tok;
     const size_t page_stride = (size_t)KH * page_size * (d + dv);
-    for (long long u = (long long)blockIdx.x * HPW_WARPS + (threadIdx.x >> 5); u < units; u += (long long)gridDim.x * HPW_WARPS) {
-        const int t = (int)(u / per_tok), idx = (int)(u % per_tok);
+    const int t = blockIdx.x;                                  // a token per grid column, its heads over grid.y and the warps
+    for (int idx = blockIdx.y * HPW_WARPS + (threadIdx.x >> 5); idx < per_tok; idx += gridDim.y * HPW_WARPS) {
         const TA* xr = x + (size_t)t * stride;
-        if (idx < QH) {
-            float v[8];
-            float ss = 0.0f;
-#pragma unroll
-            for (int m = 0; m < 8; ++m) { const int i = lane + 32 * m; v[m] = i < d ? to_f32(xr[idx * d + i]) : 0.0f; ss += v[m] * v[m]; }
-            ss = warp_sum(ss);
-            float f = 1.0f / sqrtf(ss / (float)d + eps);
-            if (temp_every > 0) f *= 1.0f + temp_coef * logf((float)((positions[t] + 1) / temp_every) + 1.0f);
-            TA* dst = q_out + ((size_t)t * QH + idx) * d;
-#pragma unroll
-            for (int m = 0; m < 8; ++m) { const int i = lane + 32 * m; if (i < d) dst[i] = from_f32<TA>(v[m] * f * to_f32(qw[i])); }
-            continue;
-        }
-        const int slot = kv_slot[t];
+        const int slot = (idx >= QH) ? kv_slot[t] : 0;
         if (slot < 0) continue;                                // a padding row of a captured step stores nothing
         const int page = slot / page_size, off = slot % page_size;
-        if (idx < QH + KH) {
-            const int hk = idx - QH;
-            const TA* src = xr + (size_t)QH * d + (size_t)hk * d;
-            float v[8];
-            float ss = 0.0f;
-#pragma unroll
-            for (int m = 0; m < 8; ++m) { const int i = lane + 32 * m; v[m] = i < d ? to_f32(src[i]) : 0.0f; ss += v[m] * v[m]; }
-            ss = warp_sum(ss);
-            const float f = 1.0f / sqrtf(ss / (float)d + eps);
-            TA* kdst = cache + (size_t)page * page_stride + ((size_t)hk * page_size + off) * d;
-            TA* vdst = cache + (size_t)page * page_stride + (size_t)KH * page_size * d + ((size_t)hk * page_size + off) * dv;
-#pragma unroll
-            for (int m = 0; m < 8; ++m) {
-                const int i = lane + 32 * m;
-                if (i < d) {
-                    kdst[i] = from_f32<TA>(v[m] * f * to_f32(kw[i]));
-                    if (values_are_keys) vdst[i] = from_f32<TA>(v[m]);
-                }
-            }
-        } else {
+        if (idx >= QH + KH) {                                  // a value head of its own: a copy
             const int hv = idx - QH - KH;
             const TA* src = xr + (size_t)(QH + KH) * d + (size_t)hv * dv;
             TA* vdst = cache + (size_t)page * page_stride + (size_t)KH * page_size * d + ((size_t)hv * page_size + off) * dv;
-            for (int i = lane; i < dv; i += 32) vdst[i] = src[i];
+            for (int i = lane * V; i < dv; i += 32 * V) { float c[V]; hp_load<V>(src + i, c); hp_store<V>(vdst + i, c); }
+            continue;
+        }
+        const bool is_q = idx < QH;
+        const int hk = idx - QH;
+        const TA* src = is_q ? xr + (size_t)idx * d : xr + (size_t)QH * d + (size_t)hk * d;
+        float v[M][V];
+        float ss = 0.0f;
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const int i = (lane + 32 * m) * V;
+            if (i < d) hp_load<V>(src + i, v[m]);
+            else {
+#pragma unroll
+                for (int c = 0; c < V; ++c) v[m][c] = 0.0f;
+            }
+#pragma unroll
+            for (int c = 0; c < V; ++c) ss += v[m][c] * v[m][c];
+        }
+        ss = warp_sum(ss);
+        float f = 1.0f / sqrtf(ss / (float)d + eps);
+        if (is_q && temp_every > 0) f *= 1.0f + temp_coef * logf((float)((positions[t] + 1) / temp_every) + 1.0f);
+        const TW* wn = is_q ? qw : kw;
+        TA* dst = is_q ? q_out + ((size_t)t * QH + idx) * d
+                       : cache + (size_t)page * page_stride + ((size_t)hk * page_size + off) * d;
+        TA* vdst = cache + (size_t)page * page_stride + (size_t)KH * page_size * d + ((size_t)hk * page_size + off) * dv;
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const int i = (lane + 32 * m) * V;
+            if (i < d) {
+                float wv[V], o[V];
+                hp_load<V>(wn + i, wv);
+#pragma unroll
+                for (int c = 0; c < V; ++c) o[c] = v[m][c] * f * wv[c];
+                hp_store<V>(dst + i, o);
+                if (!is_q && values_are_keys) hp_store<V>(vdst + i, v[m]);
+            }
         }
     }
 }
@@ -178,11 +217,17 @@ extern "C" int rb_norm_heads_append(const void* x, long long stride, int dtype, 
     cudaStream_t s = (cudaStream_t)stream;
     if (q_group == d && (!kv_slot || k_group == d) && d <= 256) {
         // norms per head: a warp per (token, head)
-        const long long units = (long long)T * (QH + (kv_slot ? KH * (values_are_keys ? 1 : 2) : 0));
-        const int blocks = (int)((units + HPW_WARPS - 1) / HPW_WARPS < 148 * 8 ? (units + HPW_WARPS - 1) / HPW_WARPS : 148 * 8);
-#define RB_HPW(TA, TW) return rb_launch(norm_heads_append_warp_kernel<TA, TW>, dim3(blocks), dim3(HPW_WARPS * 32), 0, s, (const TA*)x, stride, \
-                                        (const TW*)qw, (const TW*)kw, positions, kv_slot, (TA*)q_out, (TA*)cache, T, QH, KH, d, dv, \
-                                        values_are_keys, page_size, eps, temp_coef, temp_every)
+        const int per_tok = QH + (kv_slot ? KH * (values_are_keys ? 1 : 2) : 0);
+        const dim3 blocks(T, (per_tok + HPW_WARPS - 1) / HPW_WARPS < 65535 ? (per_tok + HPW_WARPS - 1) / HPW_WARPS : 65535);
+#define RB_HPW(TA, TW) do { \
+            if (vec4) return rb_launch(norm_heads_append_warp_kernel<TA, TW, 4, 2>, blocks, dim3(HPW_WARPS * 32), 0, s, (const TA*)x, stride, \
+                                       (const TW*)qw, (const TW*)kw, positions, kv_slot, (TA*)q_out, (TA*)cache, T, QH, KH, d, dv, \
+                                       values_are_keys, page_size, eps, temp_coef, temp_every); \
+            return rb_launch(norm_heads_append_warp_kernel<TA, TW, 1, 8>, blocks, dim3(HPW_WARPS * 32), 0, s, (const TA*)x, stride, \
+                             (const TW*)qw, (const TW*)kw, positions, kv_slot, (TA*)q_out, (TA*)cache, T, QH, KH, d, dv, \
+                             values_are_keys, page_size, eps, temp_coef, temp_every); } while (0)
+        const bool vec4 = d % 4 == 0 && dv % 4 == 0 && stride % 4 == 0 &&
+            (((uintptr_t)x | (uintptr_t)q_out | (uintptr_t)cache | (uintptr_t)qw | (uintptr_t)kw) & 15) == 0;
         if (dtype == RB_F32 && w_dtype == RB_F32) RB_HPW(float, float);
         if (dtype == RB_BF16 && w_dtype == RB_BF16) RB_HPW(bf16, bf16);
         if (dtype == RB_BF16 && w_dtype == RB_F32) RB_HPW(bf16, float);

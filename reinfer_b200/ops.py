@@ -300,7 +300,7 @@ def paged_attention_ref(q: torch.Tensor, cache: torch.Tensor, block_table: torch
     """The plain attention over the paged cache.  dv: the value heads' size where it differs from d (the cache of a
     layer is then [page][K: KH x page x d | V: KH x page x dv]); chunk: a token sees only the keys of its own chunk
     of that many positions; penalty = (r1, r2), float32 [QH] each: score -= r1 ln(1 + r2 (i - j)); out_scale
-    multiplies the output before it is rounded; bias: float32 [rows, QH], score += bias[min(i - j, rows - 1), h]."""
+    multiplies the output before it is rounded; bias: float32 [QH, rows], score += bias[h, min(i - j, rows - 1)]."""
     _need(q.is_contiguous() and out.is_contiguous() and cache.is_contiguous() and block_table.is_contiguous(),
           "attention: contiguous")
     _need(q.dtype == cache.dtype == out.dtype, "attention: one dtype for q, cache and out")
@@ -317,12 +317,13 @@ def paged_attention_ref(q: torch.Tensor, cache: torch.Tensor, block_table: torch
 
 
 def _bias_args(bias, QH: int):
-    """(pointer, rows) of a distance-bias table: float32 [rows, QH], the last row for every greater distance."""
+    """(pointer, rows) of a distance-bias table: float32 [QH, rows] (a head's biases by distance lie side by side), the
+    last entry of a head for every greater distance."""
     if bias is None:
         return c_void_p(0), c_int(0)
-    _need(bias.dtype == torch.float32 and bias.is_contiguous() and bias.dim() == 2 and bias.shape[1] == QH and bias.shape[0] > 0,
-          "attention: the distance bias is a float32 table [rows, query heads]")
-    return _p(bias), c_int(bias.shape[0])
+    _need(bias.dtype == torch.float32 and bias.is_contiguous() and bias.dim() == 2 and bias.shape[0] == QH and bias.shape[1] > 0,
+          "attention: the distance bias is a float32 table [query heads, distances]")
+    return _p(bias), c_int(bias.shape[1])
 
 
 def fa_group_chunk(group: int) -> int:
@@ -1111,7 +1112,7 @@ def rows_axpy(dst: torch.Tensor, a: torch.Tensor, src: torch.Tensor, store: bool
 def biased_attention(ctx, q: torch.Tensor, cache: torch.Tensor, group, out: torch.Tensor, QH: int, KH: int, dk: int, dv: int,
                      window: int, scale: float, bias: Optional[torch.Tensor]) -> None:
     """Softmax attention of a step's tokens over their requests' pages, causal or in a sliding window, with a
-    learned bias by distance (float32 [rows, QH]; the last row serves every greater distance) added to the scaled
+    learned bias by distance (float32 [QH, rows]; a head's last entry serves every greater distance) added to the scaled
     scores, and value heads of their own size.  q [T, QH, dk], out [T, QH, dv]."""
     n_dec, E = ctx.n_decode, ctx.n_entries
     dec_work = pre_work = (0.0, 0.0)

@@ -10,7 +10,7 @@ distance up to `bias_max`, and the last row takes every greater distance:
               = min(B - 1, B // 2 + floor(ln(n / (B // 2)) / ln(bias_max / (B // 2)) * (B - B // 2)))   otherwise
 
 At load the table is unrolled over the distances 0..bias_max (every distance from bias_max on reads the last
-row), so that the kernels index it by min(i - j, bias_max) and know nothing of buckets.
+row), and turned head-major, so that the kernels index a head's row by min(i - j, bias_max) and know nothing of buckets.
 
 Queries and keys pass an RMS norm with a plain weight: per head with one weight [dim] for all heads
 (`qk_norm="head"`), or over the whole projection at once with a weight of that size (`"whole"`).  The queries may
@@ -100,7 +100,7 @@ class BiasedAttention(Mixer):
         self.kw = t["k.norm"].to(self.qw.dtype) if self.own_kv else None
         rel = t["rel"].float()
         idx = torch.tensor(self.row_of_distance, dtype=torch.long, device=rel.device)
-        self.bias = rel.index_select(0, idx).contiguous()              # [bias_max + 1, QH] float32
+        self.bias = rel.index_select(0, idx).t().contiguous()          # [QH, bias_max + 1] float32: a head's distances side by side
 
     def forward(self, ctx, xn, residual, cache):
         T, QH, KH, dk, dv = xn.shape[0], self.QH, self.KH, self.dk, self.dv

@@ -140,7 +140,7 @@ def _paged(k, v, page, KH, dk, dv, pages_total, table):
 
 def _bias_table(rel, far):
     rows = rel.shape[0]
-    return torch.stack([rel[plain.distance_bucket(n, rows, far)] for n in range(far + 1)]).float().contiguous()
+    return torch.stack([rel[plain.distance_bucket(n, rows, far)] for n in range(far + 1)]).float().t().contiguous()     # [heads, distances]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
