@@ -264,6 +264,14 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const FcArgs a)
             const uint4 v = *reinterpret_cast<const uint4*>(a.q + ((size_t)(tok_base + row / a.Gc) * a.QH + head0 + row % a.Gc) * FC_D + c * 8);
             *reinterpret_cast<uint4*>(sQ + (row >> 7) * 2 * FC_QHALF + fc_off(row & 127, c, FC_QHALF)) = v;
         }
+        if (a.window > 0) {
+            // With a window the first key tile of a row block may hold pages that went back to the pool: their copies
+            // are skipped and their keys masked, but the values at those places are multiplied all the same (by P = 0,
+            // and 0 x NaN is NaN).  So the stages' value halves start as zeros; what a later use leaves there is this
+            // request's own finite data.
+            for (int i = threadIdx.x; i < FC_NST * (FC_KV_BYTES / 16); i += FC_THREADS)
+                *reinterpret_cast<uint4*>(stages + (i / (FC_KV_BYTES / 16)) * FC_STAGE + FC_KV_BYTES + (i % (FC_KV_BYTES / 16)) * 16) = make_uint4(0, 0, 0, 0);
+        }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();

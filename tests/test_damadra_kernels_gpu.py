@@ -209,34 +209,42 @@ def test_biased_attention_sees_what_it_should(dtype, QH, KH, dk, dv, window, pag
             assert (ref[i, 0] - v[i - window + 1, 0].double()).abs().max() < 1e-3 * v.abs().max()
 
 
-def test_pages_behind_the_window_are_not_read():
+@pytest.mark.parametrize("d,page,window", [(16, 8, 11), (128, 16, 8), (128, 64, 40), (64, 16, 20)])
+def test_pages_behind_the_window_are_not_read(d, page, window):
     """A windowed request whose early pages went back to the pool (-1 in its table; the pool's memory holds NaN there):
-    nothing of them reaches the result, in a portion and in single tokens, in both kernels."""
+    nothing of them reaches the result, in a portion and in single tokens, in every kernel - also not through what an
+    earlier launch left in shared memory (a launch over a cache of NaN runs first: a skipped copy must not leave its
+    place in a tile to whatever was there)."""
     from reinfer_b200 import ops
-    g = _gen(3)
-    QH, KH, d, window, page, n = 4, 2, 16, 11, 8, 90
+    g = _gen(3 + d)
+    QH, KH, n = 4, 2, 200
     for dtype in (torch.float32, torch.bfloat16):
         q = torch.randn(n, QH, d, generator=g).to(dtype)
         k = torch.randn(n, KH, d, generator=g).to(dtype)
         v = torch.randn(n, KH, d, generator=g).to(dtype)
         rel = torch.randn(8, QH, generator=g)
-        lo = 70                                               # tokens 70.. are run; keys before 70 - 10 are out of every window
+        lo = 150                                              # tokens 150.. are run; keys before 150 - window + 1 are out of every window
         table = list(range(-(-n // page)))
         for p in range((lo - window + 1) // page):
             table[p] = -1
+        assert table[(lo - window + 1) // page] >= 0
         cache = _paged(k, v, page, KH, d, d, len(table), table).to(DEV)
+        poison = torch.full_like(cache, float("nan"))
         bt = torch.tensor([table], dtype=torch.int32, device=DEV)
-        group = SimpleNamespace(block_table=bt, page_size=page)
+        full = torch.arange(len(table), dtype=torch.int32, device=DEV).view(1, -1)
         bias = _bias_table(rel, 30).to(DEV)
         ref = plain.softmax_attention(q.double(), k.double(), v.double(), 0.25, plain.distance_bias(n, rel.double(), 30), window)
-        for a, b in ((lo, n), (lo, lo + 1), (n - 1, n)):
+        for a, b in ((lo, n), (lo, lo + 1), (n - 1, n), (lo + 3, lo + 9)):
             T = b - a
             ctx = SimpleNamespace(tok_entry=torch.zeros(T, dtype=torch.int32, device=DEV),
                                   positions=torch.arange(a, b, dtype=torch.int32, device=DEV), n_decode=1 if T == 1 else 0, n_entries=1,
                                   q_start=[0, T], start_pos=[a], max_kv_len=b, decode_kv_tiles=None,
                                   cu_q=torch.tensor([0, T], dtype=torch.int32, device=DEV), kv_len=torch.tensor([b], dtype=torch.int32, device=DEV))
             out = torch.empty(T, QH, d, dtype=dtype, device=DEV)
-            ops.biased_attention(ctx, q[a:b].contiguous().to(DEV), cache, group, out, QH, KH, d, d, window, 0.25, bias)
+            ops.biased_attention(ctx, q[a:b].contiguous().to(DEV), poison, SimpleNamespace(block_table=full, page_size=page), out, QH, KH, d, d,
+                                 window, 0.25, bias)
+            ops.biased_attention(ctx, q[a:b].contiguous().to(DEV), cache, SimpleNamespace(block_table=bt, page_size=page), out, QH, KH, d, d,
+                                 window, 0.25, bias)
             err = (out.double().cpu() - ref[a:b]).abs().max()
             assert err <= (1e-5 if dtype == torch.float32 else 2e-2) * ref.abs().max(), (dtype, a, b, err)
 
