@@ -314,7 +314,7 @@ def silutar_shape(width: int, heads: int, ff: int, layers: int, vocab: int = 327
 
 
 def damadra_shape(width: int, heads: int, ff: int, layers: int, vocab: int = 32768, window: int = 1024, head_dim: int = 128,
-                  kv_heads: int = 0, experts: int = 8, identity: int = 4, top: int = 4) -> Dict:
+                  kv_heads: int = 0, experts: int = 8, identity: int = 2, top: int = 3) -> Dict:
     """A Damadra config.json at layer sizes that resemble a real model's: `layers` layers that cycle through a causal
     layer, a windowed layer and a causal layer that reads the keys and values of the causal layer two before it; dense
     feed-forwards of `ff` alternate with mixtures of `experts` experts of ff / 4 (plus identity experts); heads of
@@ -329,12 +329,12 @@ def damadra_shape(width: int, heads: int, ff: int, layers: int, vocab: int = 327
         if i % 3 == 1:
             layer = {"type": "attention", "mixer": dict(base, mask={"size": window})}
         else:
-            layer = {"type": "attention_2", "mixer": dict(base, q_temp={"coef": 0.3, "every": 64})}
+            layer = {"type": "attention_2", "mixer": dict(base, q_temp={"coef": 0.25, "every": 128})}
             if i % 3 == 2:
                 layer["mixer"]["kv_from"] = i - 2
         out.append(dict(layer, mlp=moe if i % 2 else dense))
     return {"architecture": "Damadra", "vocab": vocab, "width": width, "embedding": {"scale": float(width) ** 0.5},
-            "norm": {"eps": 1e-6}, "residual_mult": 0.5, "layers": out}
+            "norm": {"eps": 1e-6}, "residual_mult": 0.4, "layers": out}
 
 
 def qwen3_shape(width: int, heads: int, ff: int, layers: int, vocab: int = 32768, head_dim: int = 128, kv_heads: int = 0,
