@@ -344,3 +344,19 @@ def test_trace_program(models, tmp_path, dtype):
             done[r] = done.get(r, 0) + len(t)
         assert row == arr.shape[0]
     compare(got, want, TOL[dtype])
+
+
+def test_command_line_generates_from_a_model_folder(models):
+    """`bin/reinfer run` on a Damadra folder: greedy ids equal the plain implementation's."""
+    model_dir = models[("A", "f32")]
+    cfg, w = plain.read_model(model_dir)
+    prompt = dt.sequences("A", lengths=[9])["r0"]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "reinfer"), "run", model_dir, "-n", "6", "-t", "0", "--dtype", "float32",
+                        "--page-size", "8"] + [str(t) for t in prompt], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    got = [int(x) for x in p.stdout.strip().splitlines()[0].split()]
+    toks = list(prompt)
+    for _ in range(6):
+        toks.append(int(plain.forward(cfg, w, toks)[-1].argmax()))
+    assert got == toks[len(prompt):]
