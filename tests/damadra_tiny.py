@@ -122,3 +122,45 @@ def sequences(which: str, lengths=None, seed=7) -> Dict[str, List[int]]:
     rnd = random.Random(seed)
     lengths = lengths or {"A": [5, 17, 33, 70, 40, 26, 51], "B": [1, 9, 24, 50, 90, 37, 64, 12], "C": [3, 44, 21, 60, 30]}[which]
     return {f"r{i}": [rnd.randrange(cfg["vocab"]) for _ in range(n)] for i, n in enumerate(lengths)}
+
+
+def random_config(seed: int) -> dict:
+    """A configuration drawn from a seed: three to six layers in any order, head counts, head sizes (also ones the
+    tensor-core kernels pad or refuse), windows from one position to beyond the requests, bias tables of few and many
+    rows, readers of earlier layers, dense and mixture feed-forwards or none."""
+    rnd = random.Random(seed)
+    width = rnd.choice([48, 64, 128, 192])
+    layers, own = [], {}
+    for i in range(rnd.randint(3, 6)):
+        kind = rnd.choice(["attention", "attention_2", "attention_2"])
+        kv = rnd.choice([1, 2, 4])
+        heads = kv * rnd.choice([1, 2, 3])
+        dim = rnd.choice([8, 12, 16, 32, 48, 64, 128])
+        rows = rnd.choice([4, 8, 16, 32])
+        far = max(rnd.choice([5, 20, 100, 128, 400]), rows // 2 + 1)
+        if kind == "attention":
+            layer = _win(heads, kv, dim, rnd.choice([dim ** -0.5, 0.2]), rnd.choice([1, 7, 16, 40, 100, 500]), far, rows)
+        else:
+            vdim = rnd.choice([8, 16, 20, 64, 128, dim])
+            temp = (rnd.choice([0.1, 0.5]), rnd.choice([1, 16, 64])) if rnd.random() < 0.7 else None
+            sig = (heads, kv, dim, vdim)
+            src = own.get(sig) if rnd.random() < 0.5 else None
+            if src is None and own and rnd.random() < 0.4:
+                sig = rnd.choice(sorted(own))
+                heads, kv, dim, vdim = sig
+                src = own[sig]
+            layer = _cau(heads, kv, dim, vdim, rnd.choice([dim ** -0.5, 0.15]), far, rows, temp=temp, kv_from=src)
+            if src is None:
+                own.setdefault(sig, i)
+        r = rnd.random()
+        if r < 0.15:
+            mlp = None
+        elif r < 0.5:
+            mlp = _dense(rnd.choice([40, 64, 96]))
+        else:
+            e, idn = rnd.choice([2, 3, 8]), rnd.choice([0, 1, 3])
+            mlp = _moe(e, idn, rnd.randint(1, min(4, e + idn)), rnd.choice([12, 32, 64]))
+        layers.append(_layer(layer, mlp))
+    return {"architecture": "Damadra", "vocab": rnd.choice([97, 300, 500]), "width": width,
+            "embedding": {"scale": rnd.choice([1.0, 2.5, 12.0])}, "norm": {"eps": rnd.choice([1e-5, 1e-6])},
+            "residual_mult": rnd.choice([0.3, 0.6, 1.0]), "layers": layers}

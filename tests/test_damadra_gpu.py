@@ -360,3 +360,37 @@ def test_command_line_generates_from_a_model_folder(models):
     for _ in range(6):
         toks.append(int(plain.forward(cfg, w, toks)[-1].argmax()))
     assert got == toks[len(prompt):]
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_configurations_under_every_cut(tmp_path, seed):
+    """Configurations drawn from a seed (tests/damadra_tiny.random_config): in 32-bit every cut within the tolerance
+    of the plain implementation and bitwise equal to the others; in bfloat16 every logit finite and the median row
+    close (a sweep of this kind found a window's released pages reaching a tensor-core kernel as stale shared memory)."""
+    import random
+    from reinfer_b200.engine import Engine
+    cfg = dt.random_config(seed)
+    rnd = random.Random(1000 + seed)
+    seqs = {f"r{i}": [rnd.randrange(cfg["vocab"]) for _ in range(n)]
+            for i, n in enumerate([rnd.randint(1, 30), rnd.randint(50, 120), rnd.randint(130, 200), rnd.randint(10, 80)])}
+    page = rnd.choice([8, 16, 64])
+    cuts = (tiny.cut_whole(seqs), tiny.cut_tail_one_by_one(seqs, tail=36), tiny.cut_portions(seqs, sizes=(37, 2, 64, 3, 70, 5, 2, 11)),
+            tiny.cut_mixed(seqs, seed=seed))
+    for dtype, store in (("float32", torch.float32), ("bfloat16", torch.bfloat16)):
+        d = dt.make_model_dir(str(tmp_path / dtype), "X", store, cfg=cfg, seed=500 + seed)
+        want = truth(d, seqs)
+        first = None
+        for steps in cuts:
+            engine = Engine.from_model_dir(d, dtype=dtype, page_size=page, max_tokens=tiny.pool_tokens_needed(steps, page), max_num_seqs=4)
+            got = run_steps(engine, steps)
+            assert engine.cache.free_pages() == engine.cache.total_pages()
+            errs = torch.tensor([(row - want[r][p]).abs().max().item() / want[r][p].abs().max().item() for (r, p), row in got.items()])
+            assert torch.isfinite(errs).all(), f"{dtype}: a logit that is not finite"
+            if dtype == "float32":
+                assert errs.max().item() <= TOL[dtype], (seed, errs.max().item())
+                if first is None:
+                    first = got
+                else:
+                    assert all(torch.equal(row, first[key]) for key, row in got.items()), "bits differ between cuts"
+            else:
+                assert errs.median().item() <= TOL[dtype], (seed, errs.median().item())
